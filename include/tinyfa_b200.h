@@ -1,0 +1,86 @@
+/*
+ * C ABI of the B200-native attention-forward library (libtinyfa_b200.so).
+ *
+ * This is the drop-in boundary for the reference's forward path: each entry point below names the
+ * reference interface it stands in for.  Plain pointers and sizes only; all tensor pointers are
+ * DEVICE pointers owned by the caller; work is enqueued asynchronously on `stream` (a cudaStream_t
+ * passed as void*, NULL = the legacy default stream); the library keeps no handle.
+ *
+ * dtype codes (reference csrc/binding/flash_attn_binding.cu:22): 1 = fp16, 2 = bf16, 3 = fp32.
+ * Every function returning int returns 0 on success or one of the TFA_B200_* codes.
+ */
+#ifndef TINYFA_B200_H_
+#define TINYFA_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TFA_B200_OK 0
+#define TFA_B200_BAD_DTYPE 1
+#define TFA_B200_BAD_HEAD_DIM 2
+#define TFA_B200_BAD_ARGUMENT 3
+#define TFA_B200_CUDA_ERROR 4
+#define TFA_B200_WRONG_DEVICE 5
+#define TFA_B200_TOO_LARGE 6
+#define TFA_B200_DEVICE_TIMEOUT 7
+
+/*
+ * Fixed-length forward.  Replaces tfa::flashAttn<DType> (reference csrc/flash_attn/flash_api.cuh:43-50)
+ * and the explicit instantiations impl::runFwd<Arch,DType,HD,Causal> it dispatches to
+ * (flash_api.cuh:17-19, csrc/flash_attn/launcher.cuh:68-81).
+ *   Q, O : [batchSize, seqLenQ,  numHeadsQ,  headDim]   K, V : [batchSize, seqLenKV, numHeadsKV, headDim]
+ * dense row-major, 16-byte aligned.  Scale is 1/sqrt(headDim); causal masking is top-left aligned
+ * (key j visible to query i iff j <= i).  O is written for every query row when seqLenKV > 0 and is
+ * left untouched when seqLenKV == 0 (reference csrc/flash_attn/mma/kernel.cuh:39-42).
+ */
+int tfa_b200_fwd(const void* Q, const void* K, const void* V, void* O, int dtype, int batchSize, int seqLenQ,
+                 int seqLenKV, int numHeadsQ, int numHeadsKV, int headDim, int isCausal, void* stream);
+
+/*
+ * Packed variable-length forward.  Replaces tfa::flashAttnVarLen<DType> (reference
+ * csrc/flash_attn/flash_api.cuh:52-60) and impl::runFwdVarlen (launcher.cuh:83-99).
+ *   Q, O : [totalQ, numHeadsQ, headDim]   K, V : [totalKV, numHeadsKV, headDim]
+ *   cuSeqLensQ / cuSeqLensKV : int32 [batchSize + 1] prefix sums, DEVICE pointers.
+ * maxSeqLenQ / maxSeqLenKV only size the launch, as in the reference (launcher.cuh:94-98).
+ * totalQ / totalKV are the row counts of the packed tensors (= cuSeqLens[batchSize]); the reference
+ * signature does not carry them, so a caller that only has the reference's arguments passes -1 and the
+ * library then reads the two totals from the device with one stream-synchronising 8-byte copy.
+ */
+int tfa_b200_fwd_varlen(const void* Q, const void* K, const void* V, void* O, const int* cuSeqLensQ,
+                        const int* cuSeqLensKV, int dtype, int batchSize, int maxSeqLenQ, int maxSeqLenKV,
+                        long long totalQ, long long totalKV, int numHeadsQ, int numHeadsKV, int headDim,
+                        int isCausal, void* stream);
+
+/* Replaces tfa::isHeadDimCompiled (reference csrc/flash_attn/config.cuh:102-131): 1 for 32/64/96/128/192/256. */
+int tfa_b200_head_dim_supported(int headDim);
+
+/*
+ * Human-readable text for the last non-zero status returned on the calling thread.  Stands in for the
+ * reference's stderr messages (reference csrc/flash_attn/utils.cuh:17-24, config.cuh:95-98).
+ */
+const char* tfa_b200_last_error_string(void);
+
+/*
+ * Synchronises the current device and reports whether any kernel of this library gave up on one of its
+ * bounded waits since the last call (TFA_B200_DEVICE_TIMEOUT) or 0.  *site, when not NULL, receives the
+ * code of the wait that gave up.  The reference never checks its launches (launcher.cuh:39); this is an
+ * addition for tests and health checks.
+ */
+int tfa_b200_device_status(int* site);
+
+/*
+ * Tuning / debugging knobs (process-wide).  No counterpart in the reference, whose tile table is fixed
+ * at compile time (csrc/flash_attn/config.cuh:133-272).
+ *   "pv_split"  0/1  issue P.V as one MMA per 64-wide head-dim slice (1) or one MMA for the whole head dim (0)
+ *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto / never / always
+ * Returns TFA_B200_BAD_ARGUMENT for an unknown name.
+ */
+int tfa_b200_set_option(const char* name, int value);
+
+const char* tfa_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TINYFA_B200_H_ */

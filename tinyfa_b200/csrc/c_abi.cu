@@ -1,0 +1,302 @@
+// extern "C" boundary of libtinyfa_b200.so: argument validation, run-time dispatch on
+// (dtype, head dim) and the per-device bookkeeping the kernels need.
+//
+// Takes the place of the reference's dispatch macros TFA_DISPATCH_KERNEL / TFA_DISPATCH_ARCH /
+// TFA_DISPATCH_HEAD_DIM (reference csrc/flash_attn/flash_api.cuh:27-41, config.cuh:86-100, 276-333):
+// where the reference turns (compute capability, head dim, causal) into template arguments and aborts
+// on an unsupported head dim, this file requires compute capability 10.x and returns status codes.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/tinyfa_b200.h"
+#include "tfa_common.cuh"
+
+namespace tfa_b200 {
+
+// ---- instantiations (fwd_tc_inst.cu, one object per pair)
+int launch_fwd_tc_hdp64_bf0(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp64_bf1(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp128_bf0(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp128_bf1(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp192_bf0(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp192_bf1(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp256_bf0(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp256_bf1(const FwdProblem&, int, int);
+
+static thread_local char g_err[512] = "";
+
+void set_error_string(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+static std::atomic<int> g_optPvSplit{0};
+static std::atomic<int> g_optPackGqa{-1};
+static std::atomic<int> g_epoch{1};
+
+int next_epoch() { return (g_epoch.fetch_add(1) & 0x7FFFFF) + 1; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess) return (EncodeTiledFn) nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  if (fn == nullptr) set_error_string("cuTensorMapEncodeTiled is not available from the driver");
+  return fn;
+}
+
+// One status word per device, allocated on first use and kept for the life of the process.
+static std::mutex g_devMutex;
+static int* g_statusWord[64] = {nullptr};
+static int g_devChecked[64] = {0};  // 0 = unknown, 1 = cc 10.x, -1 = other
+
+int* device_status_word(int device) {
+  std::lock_guard<std::mutex> lock(g_devMutex);
+  if (device < 0 || device >= 64) return nullptr;
+  if (g_statusWord[device] == nullptr) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess || cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+      set_error_string("could not allocate the device status word: %s", cudaGetErrorString(cudaGetLastError()));
+      return nullptr;
+    }
+    g_statusWord[device] = p;
+  }
+  return g_statusWord[device];
+}
+
+static int check_device() {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) {
+    set_error_string("cudaGetDevice: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  if (device < 0 || device >= 64) return kBadArgument;
+  std::lock_guard<std::mutex> lock(g_devMutex);
+  if (g_devChecked[device] == 0) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (e != cudaSuccess) {
+      set_error_string("cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+      return kCudaError;
+    }
+    g_devChecked[device] = (major == 10) ? 1 : -1;
+  }
+  if (g_devChecked[device] != 1) {
+    set_error_string("device %d is not compute capability 10.x; this library contains sm_100a code only", device);
+    return kWrongDevice;
+  }
+  return kOk;
+}
+
+static bool head_dim_ok(int d) { return d == 32 || d == 64 || d == 96 || d == 128 || d == 192 || d == 256; }
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int pick_pack_shift(const FwdProblem& p) {
+  const int group = p.headsQ / p.headsKV;
+  int shift = 0;
+  while (((group >> (shift + 1)) << (shift + 1)) == group && (1 << (shift + 1)) <= 128) shift++;  // pow-2 part
+  const int opt = g_optPackGqa.load();
+  if (opt == 0 || shift == 0) return 0;
+  if (opt == 1) return shift;
+  return (p.seqLenQ < 128) ? shift : 0;  // auto: short query blocks share one tile across the group's heads
+}
+
+static int dispatch(const FwdProblem& p) {
+  if (p.dtype == kFp32) return launch_fwd_fp32(p);
+  const bool bf = (p.dtype == kBf16);
+  const int ps = pick_pack_shift(p);
+  const int split = g_optPvSplit.load();
+  switch (p.headDim) {
+    case 32:
+    case 64:
+      return bf ? launch_fwd_tc_hdp64_bf1(p, ps, split) : launch_fwd_tc_hdp64_bf0(p, ps, split);
+    case 96:
+    case 128:
+      return bf ? launch_fwd_tc_hdp128_bf1(p, ps, split) : launch_fwd_tc_hdp128_bf0(p, ps, split);
+    case 192:
+      return bf ? launch_fwd_tc_hdp192_bf1(p, ps, split) : launch_fwd_tc_hdp192_bf0(p, ps, split);
+    case 256:
+      return bf ? launch_fwd_tc_hdp256_bf1(p, ps, split) : launch_fwd_tc_hdp256_bf0(p, ps, split);
+    default:
+      return kBadHeadDim;
+  }
+}
+
+static int validate_common(const void* Q, const void* K, const void* V, void* O, int dtype, int batch, int sq, int skv,
+                           int hq, int hkv, int d) {
+  if (dtype != kFp16 && dtype != kBf16 && dtype != kFp32) {
+    set_error_string("unsupported dtype code %d (1 = fp16, 2 = bf16, 3 = fp32)", dtype);
+    return kBadDtype;
+  }
+  if (!head_dim_ok(d)) {
+    set_error_string("TinyFA: unsupported headDim: %d", d);
+    return kBadHeadDim;
+  }
+  if (batch < 0 || sq < 0 || skv < 0 || hq <= 0 || hkv <= 0) {
+    set_error_string("negative size or non-positive head count (batch=%d seqQ=%d seqKV=%d Hq=%d Hkv=%d)", batch, sq,
+                     skv, hq, hkv);
+    return kBadArgument;
+  }
+  if (hq % hkv != 0) {
+    set_error_string("numHeadsQ (%d) must be divisible by numHeadsKV (%d)", hq, hkv);
+    return kBadArgument;
+  }
+  if (batch > 65535 || hq > 65535) {
+    set_error_string("batchSize and numHeadsQ are limited to 65535 (grid dimensions)");
+    return kTooLarge;
+  }
+  if (batch > 0 && sq > 0 && (Q == nullptr || O == nullptr || (skv > 0 && (K == nullptr || V == nullptr)))) {
+    set_error_string("null tensor pointer");
+    return kBadArgument;
+  }
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) {
+    set_error_string("Q, K, V and O must be 16-byte aligned");
+    return kBadArgument;
+  }
+  return kOk;
+}
+
+}  // namespace tfa_b200
+
+using namespace tfa_b200;
+
+extern "C" int tfa_b200_fwd(const void* Q, const void* K, const void* V, void* O, int dtype, int batchSize,
+                            int seqLenQ, int seqLenKV, int numHeadsQ, int numHeadsKV, int headDim, int isCausal,
+                            void* stream) {
+  int rc = validate_common(Q, K, V, O, dtype, batchSize, seqLenQ, seqLenKV, numHeadsQ, numHeadsKV, headDim);
+  if (rc != kOk) return rc;
+  if (batchSize == 0 || seqLenQ == 0 || seqLenKV == 0) return kOk;  // nothing to write
+  if ((long long)batchSize * seqLenQ > 0x7FFFFFFFll || (long long)batchSize * seqLenKV > 0x7FFFFFFFll) {
+    set_error_string("batchSize * seqLen must stay below 2^31 rows");
+    return kTooLarge;
+  }
+  if ((rc = check_device()) != kOk) return rc;
+  FwdProblem p;
+  p.Q = Q;
+  p.K = K;
+  p.V = V;
+  p.O = O;
+  p.cuQ = nullptr;
+  p.cuKV = nullptr;
+  p.dtype = dtype;
+  p.batch = batchSize;
+  p.seqLenQ = seqLenQ;
+  p.seqLenKV = seqLenKV;
+  p.totalQ = (long long)batchSize * seqLenQ;
+  p.totalKV = (long long)batchSize * seqLenKV;
+  p.headsQ = numHeadsQ;
+  p.headsKV = numHeadsKV;
+  p.headDim = headDim;
+  p.causal = isCausal ? 1 : 0;
+  p.stream = static_cast<cudaStream_t>(stream);
+  return dispatch(p);
+}
+
+extern "C" int tfa_b200_fwd_varlen(const void* Q, const void* K, const void* V, void* O, const int* cuSeqLensQ,
+                                   const int* cuSeqLensKV, int dtype, int batchSize, int maxSeqLenQ, int maxSeqLenKV,
+                                   long long totalQ, long long totalKV, int numHeadsQ, int numHeadsKV, int headDim,
+                                   int isCausal, void* stream) {
+  int rc = validate_common(Q, K, V, O, dtype, batchSize, maxSeqLenQ, maxSeqLenKV, numHeadsQ, numHeadsKV, headDim);
+  if (rc != kOk) return rc;
+  if (batchSize == 0 || maxSeqLenQ == 0 || maxSeqLenKV == 0) return kOk;
+  if (cuSeqLensQ == nullptr || cuSeqLensKV == nullptr) {
+    set_error_string("null cu_seqlens pointer");
+    return kBadArgument;
+  }
+  if ((rc = check_device()) != kOk) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (totalQ < 0 || totalKV < 0) {
+    int tq = 0, tkv = 0;
+    cudaError_t e = cudaMemcpyAsync(&tq, cuSeqLensQ + batchSize, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&tkv, cuSeqLensKV + batchSize, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+      set_error_string("reading cu_seqlens totals: %s", cudaGetErrorString(e));
+      return kCudaError;
+    }
+    totalQ = tq;
+    totalKV = tkv;
+  }
+  if (totalQ == 0 || totalKV == 0) return kOk;
+  if (totalQ > 0x7FFFFFFFll || totalKV > 0x7FFFFFFFll) return kTooLarge;
+  FwdProblem p;
+  p.Q = Q;
+  p.K = K;
+  p.V = V;
+  p.O = O;
+  p.cuQ = cuSeqLensQ;
+  p.cuKV = cuSeqLensKV;
+  p.dtype = dtype;
+  p.batch = batchSize;
+  p.seqLenQ = maxSeqLenQ;
+  p.seqLenKV = maxSeqLenKV;
+  p.totalQ = totalQ;
+  p.totalKV = totalKV;
+  p.headsQ = numHeadsQ;
+  p.headsKV = numHeadsKV;
+  p.headDim = headDim;
+  p.causal = isCausal ? 1 : 0;
+  p.stream = s;
+  return dispatch(p);
+}
+
+extern "C" int tfa_b200_head_dim_supported(int headDim) { return head_dim_ok(headDim) ? 1 : 0; }
+
+extern "C" const char* tfa_b200_last_error_string(void) { return g_err; }
+
+extern "C" int tfa_b200_device_status(int* site) {
+  if (site != nullptr) *site = 0;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return kCudaError;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_error_string("cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  int* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_devMutex);
+    if (device >= 0 && device < 64) word = g_statusWord[device];
+  }
+  if (word == nullptr) return kOk;  // no kernel of this library has run on this device yet
+  int v = 0;
+  if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return kCudaError;
+  if (v == 0) return kOk;
+  cudaMemset(word, 0, sizeof(int));
+  if (site != nullptr) *site = v & 0xFF;
+  set_error_string("a kernel gave up on a bounded wait (site %d, launch epoch %d)", v & 0xFF, v >> 8);
+  return kDeviceTimeout;
+}
+
+extern "C" int tfa_b200_set_option(const char* name, int value) {
+  if (name == nullptr) return kBadArgument;
+  if (strcmp(name, "pv_split") == 0) {
+    g_optPvSplit.store(value ? 1 : 0);
+    return kOk;
+  }
+  if (strcmp(name, "pack_gqa") == 0) {
+    g_optPackGqa.store(value < 0 ? -1 : (value ? 1 : 0));
+    return kOk;
+  }
+  set_error_string("unknown option '%s'", name);
+  return kBadArgument;
+}
+
+extern "C" const char* tfa_b200_version(void) { return "tinyfa_b200 0.1 (sm_100a)"; }

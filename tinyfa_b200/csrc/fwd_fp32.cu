@@ -1,0 +1,330 @@
+// FP32 attention forward on CUDA cores (true fp32 FMAs, no TF32), for sm_100a.
+//
+// Takes the place of the reference's FMA kernel for DType = float (reference
+// csrc/flash_attn/fma/kernel.cuh:83-240) with the same contract: inputs and accumulators are fp32
+// (fma/gemm.cuh:94-98, 162-166), scale 1/sqrt(D) folded into exp2, top-left causal mask and
+// "col >= seqLenKV" mask (fma/softmax.cuh:97-99), row sum 0 -> output 0 (fma/softmax.cuh:76),
+// sequences without keys leave O untouched (fma/kernel.cuh:116-119).
+//
+// One CTA (128 threads) owns BR query rows of one (batch, Q head) and streams 64-key blocks.
+// Thread (ty, tx) = (tid / 8, tid % 8) owns RPT = BR/16 rows; in S it owns the 8 columns tx + 8*i, in O
+// the float4 chunks tx + 8*i of the head dim.  K and V blocks are staged with 16-byte cp.async into
+// padded rows (row stride D + 4 floats keeps the float4 reads of 8 neighbouring threads on distinct
+// banks); V(j) streams in under S(j) and K(j+1) under P.V(j).
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "tfa_common.cuh"
+
+namespace tfa_b200 {
+
+struct Fp32Params {
+  const float* Q;
+  const float* K;
+  const float* V;
+  float* O;
+  const int* cuQ;
+  const int* cuKV;
+  int seqLenQ;
+  int seqLenKV;
+  int headsQ;
+  int headsKV;
+  int group;
+  int causal;
+  float scaleLog2;
+};
+
+namespace fp32 {
+
+constexpr int kThreads = 128;
+constexpr int kBC = 64;
+
+__device__ __forceinline__ void cp_async16(float* smemDst, const float* gmemSrc, bool valid) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smemDst));
+  const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmemSrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// rows [row0, row0 + ROWS) of one head -> smem tile with row stride LD; rows >= rowEnd are zero-filled.
+template <int D, int ROWS, int LD>
+__device__ __forceinline__ void load_tile(float* sm, const float* base, long long row0, long long rowEnd,
+                                          long long rowStride) {
+  constexpr int kChunks = ROWS * (D / 4);
+  for (int i = threadIdx.x; i < kChunks; i += kThreads) {
+    const int r = i / (D / 4), c = i % (D / 4);
+    const bool valid = (row0 + r) < rowEnd;
+    const float* src = base + (valid ? (row0 + r) : row0) * rowStride + c * 4;
+    cp_async16(sm + r * LD + c * 4, valid ? src : base, valid);
+  }
+}
+
+template <int D, int BR>
+__global__ void __launch_bounds__(kThreads) fwd_fp32_kernel(const Fp32Params p) {
+  constexpr int LD = D + 4;
+  constexpr int LDP = kBC + 4;
+  constexpr int RPT = BR / 16;
+  constexpr int NCH = D / 32;
+  extern __shared__ float4 smemF4[];
+  float* sQ = reinterpret_cast<float*>(smemF4);
+  float* sK = sQ + BR * LD;
+  float* sV = sK + kBC * LD;
+  float* sP = sV + kBC * LD;
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int hkv = h / p.group;
+  long long qRow0, kvRow0;
+  int sq, skv;
+  if (p.cuQ != nullptr) {
+    qRow0 = p.cuQ[b];
+    sq = p.cuQ[b + 1] - p.cuQ[b];
+    kvRow0 = p.cuKV[b];
+    skv = p.cuKV[b + 1] - p.cuKV[b];
+  } else {
+    sq = p.seqLenQ;
+    skv = p.seqLenKV;
+    qRow0 = (long long)b * sq;
+    kvRow0 = (long long)b * skv;
+  }
+  const int numTilesQ = gridDim.x;
+  const int tileIdx = p.causal ? (numTilesQ - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const int q0 = tileIdx * BR;
+  if (q0 >= sq || skv <= 0) return;
+  const int qEnd = min(q0 + BR, sq);
+  int nblk = (skv + kBC - 1) / kBC;
+  if (p.causal) nblk = min(nblk, (qEnd + kBC - 1) / kBC);
+
+  const long long qStride = (long long)p.headsQ * D;
+  const long long kvStride = (long long)p.headsKV * D;
+  const float* gQ = p.Q + (long long)h * D;
+  const float* gK = p.K + (long long)hkv * D;
+  const float* gV = p.V + (long long)hkv * D;
+
+  const int ty = threadIdx.x >> 3, tx = threadIdx.x & 7;
+
+  load_tile<D, BR, LD>(sQ, gQ, qRow0 + q0, qRow0 + sq, qStride);
+  load_tile<D, kBC, LD>(sK, gK, kvRow0, kvRow0 + skv, kvStride);
+  cp_async_commit();
+
+  float o[RPT][NCH][4];
+  float m[RPT], l[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; r++) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; i++) {
+      o[r][i][0] = o[r][i][1] = o[r][i][2] = o[r][i][3] = 0.f;
+    }
+  }
+  const float c = p.scaleLog2;
+
+  for (int j = 0; j < nblk; j++) {
+    const int kbase = j * kBC;
+    load_tile<D, kBC, LD>(sV, gV, kvRow0 + kbase, kvRow0 + skv, kvStride);
+    cp_async_commit();
+    cp_async_wait<1>();  // Q and K(j) have landed
+    __syncthreads();
+
+    // ---- S = Q K^T for rows ty*RPT.., columns tx + 8*i
+    float s[RPT][8];
+#pragma unroll
+    for (int r = 0; r < RPT; r++) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) s[r][i] = 0.f;
+    }
+#pragma unroll 4
+    for (int d4 = 0; d4 < D / 4; d4++) {
+      float4 q[RPT];
+#pragma unroll
+      for (int r = 0; r < RPT; r++) q[r] = *reinterpret_cast<const float4*>(sQ + (ty * RPT + r) * LD + d4 * 4);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float4 k = *reinterpret_cast<const float4*>(sK + (tx + 8 * i) * LD + d4 * 4);
+#pragma unroll
+        for (int r = 0; r < RPT; r++) {
+          s[r][i] = fmaf(q[r].x, k.x, s[r][i]);
+          s[r][i] = fmaf(q[r].y, k.y, s[r][i]);
+          s[r][i] = fmaf(q[r].z, k.z, s[r][i]);
+          s[r][i] = fmaf(q[r].w, k.w, s[r][i]);
+        }
+      }
+    }
+
+    // ---- mask + online softmax
+    const bool needMask = (kbase + kBC > skv) || (p.causal && (kbase + kBC - 1 > q0));
+#pragma unroll
+    for (int r = 0; r < RPT; r++) {
+      const int qpos = q0 + ty * RPT + r;
+      if (needMask) {
+        int lim = skv - kbase;
+        if (p.causal) lim = min(lim, qpos - kbase + 1);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          if (tx + 8 * i >= lim) s[r][i] = -INFINITY;
+        }
+      }
+      float mx = s[r][0];
+#pragma unroll
+      for (int i = 1; i < 8; i++) mx = fmaxf(mx, s[r][i]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float mNew = fmaxf(m[r], mx);
+      const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
+      const float scale = (m[r] == -INFINITY) ? 0.f : ex2((m[r] - mUse) * c);
+      m[r] = mNew;
+      const float negMc = -mUse * c;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float pv = ex2(fmaf(s[r][i], c, negMc));
+        sum += pv;
+        sP[(ty * RPT + r) * LDP + tx + 8 * i] = pv;
+      }
+      l[r] = l[r] * scale + sum;  // per-thread partial row sum, reduced over tx at the end
+#pragma unroll
+      for (int i = 0; i < NCH; i++) {
+        o[r][i][0] *= scale;
+        o[r][i][1] *= scale;
+        o[r][i][2] *= scale;
+        o[r][i][3] *= scale;
+      }
+    }
+
+    cp_async_wait<0>();  // V(j) has landed
+    __syncthreads();     // ... and P is visible, and nobody still reads K(j)
+    if (j + 1 < nblk) {
+      load_tile<D, kBC, LD>(sK, gK, kvRow0 + kbase + kBC, kvRow0 + skv, kvStride);
+    }
+    cp_async_commit();
+
+    // ---- O += P V
+#pragma unroll 2
+    for (int c4 = 0; c4 < kBC / 4; c4++) {
+      float pr[RPT][4];
+#pragma unroll
+      for (int r = 0; r < RPT; r++) {
+        const float4 t = *reinterpret_cast<const float4*>(sP + (ty * RPT + r) * LDP + c4 * 4);
+        pr[r][0] = t.x;
+        pr[r][1] = t.y;
+        pr[r][2] = t.z;
+        pr[r][3] = t.w;
+      }
+#pragma unroll
+      for (int cc = 0; cc < 4; cc++) {
+#pragma unroll
+        for (int i = 0; i < NCH; i++) {
+          const float4 v = *reinterpret_cast<const float4*>(sV + (c4 * 4 + cc) * LD + (tx + 8 * i) * 4);
+#pragma unroll
+          for (int r = 0; r < RPT; r++) {
+            o[r][i][0] = fmaf(pr[r][cc], v.x, o[r][i][0]);
+            o[r][i][1] = fmaf(pr[r][cc], v.y, o[r][i][1]);
+            o[r][i][2] = fmaf(pr[r][cc], v.z, o[r][i][2]);
+            o[r][i][3] = fmaf(pr[r][cc], v.w, o[r][i][3]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // P and V(j) are free again
+  }
+  cp_async_wait<0>();
+
+  // ---- normalise and store
+#pragma unroll
+  for (int r = 0; r < RPT; r++) {
+    float sum = l[r];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    const float inv = (sum > 0.f) ? (1.f / sum) : 0.f;
+    const int qpos = q0 + ty * RPT + r;
+    if (qpos < sq) {
+      float* dst = p.O + (qRow0 + qpos) * qStride + (long long)h * D;
+#pragma unroll
+      for (int i = 0; i < NCH; i++) {
+        float4 v;
+        v.x = o[r][i][0] * inv;
+        v.y = o[r][i][1] * inv;
+        v.z = o[r][i][2] * inv;
+        v.w = o[r][i][3] * inv;
+        *reinterpret_cast<float4*>(dst + (tx + 8 * i) * 4) = v;
+      }
+    }
+  }
+}
+
+template <int D, int BR>
+int launch(const FwdProblem& pr) {
+  constexpr int LD = D + 4;
+  constexpr int kSmem = (BR * LD + 2 * kBC * LD + BR * (kBC + 4)) * (int)sizeof(float);
+  auto kernel = fwd_fp32_kernel<D, BR>;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return kCudaError;
+  static std::once_flag once[64];
+  static cudaError_t attrErr[64];
+  std::call_once(once[device], [&] {
+    attrErr[device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  });
+  if (attrErr[device] != cudaSuccess) {
+    set_error_string("cudaFuncSetAttribute(%d bytes): %s", kSmem, cudaGetErrorString(attrErr[device]));
+    return kCudaError;
+  }
+  Fp32Params p;
+  p.Q = static_cast<const float*>(pr.Q);
+  p.K = static_cast<const float*>(pr.K);
+  p.V = static_cast<const float*>(pr.V);
+  p.O = static_cast<float*>(pr.O);
+  p.cuQ = pr.cuQ;
+  p.cuKV = pr.cuKV;
+  p.seqLenQ = pr.seqLenQ;
+  p.seqLenKV = pr.seqLenKV;
+  p.headsQ = pr.headsQ;
+  p.headsKV = pr.headsKV;
+  p.group = pr.headsQ / pr.headsKV;
+  p.causal = pr.causal;
+  p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)D));
+  dim3 grid((unsigned)((pr.seqLenQ + BR - 1) / BR), (unsigned)pr.headsQ, (unsigned)pr.batch);
+  kernel<<<grid, kThreads, kSmem, pr.stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error_string("fp32 kernel launch failed: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  return kOk;
+}
+
+}  // namespace fp32
+
+int launch_fwd_fp32(const FwdProblem& pr) {
+  switch (pr.headDim) {
+    case 32:
+      return fp32::launch<32, 64>(pr);
+    case 64:
+      return fp32::launch<64, 64>(pr);
+    case 96:
+      return fp32::launch<96, 64>(pr);
+    case 128:
+      return fp32::launch<128, 64>(pr);
+    case 192:
+      return fp32::launch<192, 32>(pr);
+    case 256:
+      return fp32::launch<256, 32>(pr);
+    default:
+      return kBadHeadDim;
+  }
+}
+
+}  // namespace tfa_b200

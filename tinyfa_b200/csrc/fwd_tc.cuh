@@ -1,0 +1,513 @@
+// FP16 / BF16 attention forward for sm_100a: TMA -> swizzled shared memory -> tcgen05.mma with
+// accumulators in tensor memory, online softmax read straight out of tensor memory, P handed to the
+// second MMA through tensor memory (no shared-memory or HBM round trip).
+//
+// Replaces the reference's mma.sync kernel (reference csrc/flash_attn/mma/kernel.cuh:18-201) and
+// keeps its contract: scale 1/sqrt(D) folded into exp2 (mma/softmax.cuh:104-108), top-left causal
+// mask "col > row" plus "col >= seqLenKV" (mma/softmax.cuh:136-138), KV head = Q head / group
+// (params.cuh:25-27), fp32 accumulation of S and O, P rounded to the 16-bit input type before P.V
+// while the row sum uses unrounded P (mma/softmax.cuh:107-108, mma/layout.cuh:87-97), a row whose
+// sum is 0 yields 0 (mma/softmax.cuh:126), sequences without keys leave O untouched
+// (mma/kernel.cuh:39-42).
+//
+// CTA = 16 warps:
+//   warps 0-3   softmax for Q tile 0 (one thread per query row, 128 rows)
+//   warps 4-7   softmax for Q tile 1 (when the CTA owns two Q tiles)
+//   warps 8-11  correction: rescales O in tensor memory when the running max moves, final 1/sum, stores O
+//   warp  12    issues every tcgen05.mma (one thread)
+//   warp  13    issues every TMA load (one thread)
+//   warps 14-15 idle (they exist so that the last warpgroup can give its registers away)
+//
+// Tensor memory columns (fp32 words per lane; lane = query row of the tile):
+//   [t*128, t*128+128)            S of Q tile t; the 16-bit P overwrites the first 64 columns
+//   [256 + t*HDP, 256+(t+1)*HDP)  O of Q tile t (NT == 2, HDP <= 128), or [128, 128+HDP) when NT == 1
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+#include "tfa_common.cuh"
+
+namespace tfa_b200 {
+
+struct TcParams {
+  void* O;
+  const int* cuQ;
+  const int* cuKV;
+  int seqLenQ;    // fixed length, or max length for varlen
+  int seqLenKV;
+  int headsQ;
+  int headsKV;
+  int headDim;    // true head dim (<= HDP)
+  int group;      // headsQ / headsKV
+  int packShift;  // log2 of the number of Q heads interleaved into one 128-row tile
+  int numPairs;   // gridDim.x
+  int causal;
+  int pvSplit;    // debug knob: 1 = issue P.V as one MMA per 64-wide slice of the head dim
+  float scaleLog2;  // log2(e) / sqrt(headDim)
+  int* status;      // device status word
+  int epoch;        // launch epoch (24 bits)
+};
+
+namespace tc {
+
+constexpr int kBlockM = 128;  // query rows per tile = TMEM lanes
+constexpr int kBlockN = 128;  // keys per KV block
+constexpr int kThreads = 512;
+constexpr int kSubTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 16-bit elements), one swizzle-128B slab
+
+template <int HDP>
+struct Cfg {
+  static constexpr int kSub = HDP / 64;                  // 64-element slabs per row
+  static constexpr int kTileBytes = kSub * kSubTileBytes;  // one 128-row tile of Q, K or V
+  static constexpr int kNT = (HDP <= 128) ? 2 : 1;       // Q tiles per CTA
+  static constexpr int kStages = (HDP == 64) ? 6 : (HDP == 128) ? 4 : (HDP == 192) ? 3 : 2;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kOCol0 = (kNT == 2) ? 256 : 128;
+  static constexpr int kSmemBytes = (kNT + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
+};
+
+// Barrier slots (8 bytes each) inside the control block that follows the tiles.
+enum Bar : int {
+  kBarQFull = 0,      // [2]  Q tile landed
+  kBarSFull = 2,      // [2]  S = Q.K^T finished (tcgen05.commit)
+  kBarPvReady = 4,    // [2]  P written (4 softmax warps) and O rescaled (4 correction warps)
+  kBarPvDone = 6,     // [2]  O += P.V finished (tcgen05.commit)
+  kBarScaleFull = 8,  // [2]  softmax published the rescale factor (or the final row sum)
+  kBarScaleEmpty = 10,  // [2] correction consumed it
+  kBarKvFull = 12,    // [kStages]
+  kBarKvEmpty = 20,   // [kStages]
+  kNumBars = 28,
+};
+
+struct Ctl {
+  uint64_t bars[kNumBars];
+  float scale[2][kBlockM];
+  uint32_t tmemBase;
+  int failed;
+};
+
+struct WaitCtx {
+  volatile int* failed;
+  int* status;
+  int epoch;
+};
+
+// Bounded wait: gives up after ~2 s, records (epoch << 8 | site) and lets the caller continue so that
+// every loop still terminates; later waits of the CTA return at once.
+__device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, const WaitCtx& c, int site) {
+  if (ptx::mbar_try_wait(bar, parity)) return;
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3FF) == 0) {
+      if (*c.failed) return;
+      const uint64_t now = ptx::global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2000000000ull) {
+        *c.failed = 1;
+        atomicExch(c.status, (c.epoch << 8) | site);
+        return;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+// Per-CTA work description, computed identically by every role.
+struct Work {
+  long long qRow0;   // first row of this sequence in Q/O
+  long long kvRow0;  // first row of this sequence in K/V
+  int sq, skv;
+  int unit;          // Q head unit (packs 1 << packShift heads)
+  int hkv;
+  int qlo[2], qhi[2];  // sequence positions covered by each tile: [qlo, qhi)
+  int nblk[2];         // KV blocks each tile consumes
+  int nmax;
+};
+
+template <int NT>
+__device__ __forceinline__ bool make_work(const TcParams& p, Work& w) {
+  const int pairIdx = p.causal ? (p.numPairs - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // heavy tiles first
+  w.unit = blockIdx.y;
+  const int b = blockIdx.z;
+  if (p.cuQ != nullptr) {
+    const int q0 = p.cuQ[b], q1 = p.cuQ[b + 1], k0 = p.cuKV[b], k1 = p.cuKV[b + 1];
+    w.qRow0 = q0;
+    w.sq = q1 - q0;
+    w.kvRow0 = k0;
+    w.skv = k1 - k0;
+  } else {
+    w.sq = p.seqLenQ;
+    w.skv = p.seqLenKV;
+    w.qRow0 = (long long)b * p.seqLenQ;
+    w.kvRow0 = (long long)b * p.seqLenKV;
+  }
+  const int rows = kBlockM >> p.packShift;  // sequence positions per tile
+  const int seq0 = pairIdx * NT * rows;
+  if (seq0 >= w.sq || w.skv <= 0) return false;
+  w.hkv = (w.unit << p.packShift) / p.group;
+  const int nTotal = (w.skv + kBlockN - 1) / kBlockN;
+  w.nmax = 0;
+#pragma unroll
+  for (int t = 0; t < 2; t++) {
+    w.qlo[t] = seq0 + t * rows;
+    w.qhi[t] = min(w.qlo[t] + rows, w.sq);
+    int n = 0;
+    if (t < NT && w.qlo[t] < w.sq) {
+      n = p.causal ? min(nTotal, (w.qhi[t] + kBlockN - 1) / kBlockN) : nTotal;
+    }
+    w.nblk[t] = n;
+    w.nmax = max(w.nmax, n);
+  }
+  return true;
+}
+
+template <int HDP, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const TcParams p) {
+  using C = Cfg<HDP>;
+  constexpr int NT = C::kNT;
+  constexpr int NS = C::kStages;
+  static_assert(NS <= 8, "barrier slots");
+
+  Work w;
+  if (!make_work<NT>(p, w)) return;  // uniform for the CTA: nothing allocated yet
+  if ((*p.status >> 8) == p.epoch) return;  // an earlier CTA of this launch already gave up: drain quickly
+
+  extern __shared__ uint8_t smemRaw[];
+  const uint32_t rawAddr = ptx::smem_u32(smemRaw);
+  const uint32_t tileAddr = (rawAddr + 1023u) & ~1023u;  // swizzle-128B slabs need 1024-byte alignment
+  uint8_t* smem = smemRaw + (tileAddr - rawAddr);
+  const uint32_t sQ = tileAddr;
+  const uint32_t sKV = tileAddr + NT * C::kTileBytes;
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + (NT + NS) * C::kTileBytes);
+  const uint32_t barBase = ptx::smem_u32(&ctl->bars[0]);
+  auto bar = [&](int slot) { return barBase + 8u * (uint32_t)slot; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; t++) {
+      ptx::mbar_init(bar(kBarQFull + t), 1);
+      ptx::mbar_init(bar(kBarSFull + t), 1);
+      ptx::mbar_init(bar(kBarPvReady + t), 8);
+      ptx::mbar_init(bar(kBarPvDone + t), 1);
+      ptx::mbar_init(bar(kBarScaleFull + t), 4);
+      ptx::mbar_init(bar(kBarScaleEmpty + t), 4);
+    }
+    for (int s = 0; s < NS; s++) {
+      ptx::mbar_init(bar(kBarKvFull + s), 1);
+      ptx::mbar_init(bar(kBarKvEmpty + s), 1);
+    }
+    ctl->failed = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 12) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmemBase), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if (warp == 13 && lane == 0) {
+    ptx::prefetch_tensormap(&tmQ);
+    ptx::prefetch_tensormap(&tmK);
+    ptx::prefetch_tensormap(&tmV);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = ctl->tmemBase;
+  const WaitCtx wc{&ctl->failed, p.status, p.epoch};
+
+  if (warp < 8) {
+    // ================================================================ softmax
+    ptx::setmaxnreg_inc<184>();
+    const int t = warp >> 2;
+    if (t < NT && w.nblk[t] > 0) {
+      const int r = threadIdx.x & 127;
+      const uint32_t tS = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(t * 128);
+      const int qpos = w.qlo[t] + (r >> p.packShift);
+      const float c = p.scaleLog2;
+      float m = -INFINITY, l = 0.f;
+      const int n = w.nblk[t];
+      for (int j = 0; j < n; j++) {
+        wait_bar(bar(kBarSFull + t), j & 1, wc, 1);
+        ptx::tc_fence_after();
+        uint32_t v[4][32];
+#pragma unroll
+        for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
+        ptx::tmem_wait_ld();
+
+        const int kbase = j * kBlockN;
+        const bool needMask = (kbase + kBlockN > w.skv) || (p.causal && (kbase + kBlockN - 1 > w.qlo[t]));
+        if (needMask) {
+          int lim = w.skv - kbase;                         // columns [0, lim) are real keys
+          if (p.causal) lim = min(lim, qpos - kbase + 1);  // ... that are not in the future
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+              if (q * 32 + i >= lim) v[q][i] = 0xff800000u;  // -inf
+            }
+          }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[q][i]));
+        }
+        const float mNew = fmaxf(m, mx);
+        const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
+        const float scale = (m == -INFINITY) ? 0.f : ex2((m - mUse) * c);
+        m = mNew;
+
+        // hand the rescale factor to the correction warps before the long exp loop
+        if (j > 0) wait_bar(bar(kBarScaleEmpty + t), (j - 1) & 1, wc, 2);
+        ctl->scale[t][r] = scale;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
+
+        const float negMc = -mUse * c;
+        float sum = 0.f;
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(v[q][i]), c, negMc));
+            const float p1 = ex2(fmaf(__uint_as_float(v[q][i + 1]), c, negMc));
+            sum += p0 + p1;
+            pk[q >> 1][(q & 1) * 16 + (i >> 1)] = pack2<kBf16>(p0, p1);
+          }
+        }
+        l = l * scale + sum;
+        ptx::tmem_st_32x32b_x32(tS, pk[0]);
+        ptx::tmem_st_32x32b_x32(tS + 32, pk[1]);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kBarPvReady + t));
+      }
+      // final row sum for the epilogue
+      wait_bar(bar(kBarScaleEmpty + t), (n - 1) & 1, wc, 3);
+      ctl->scale[t][r] = l;
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
+    }
+  } else if (warp < 12) {
+    // ================================================================ correction + epilogue
+    ptx::setmaxnreg_dec<88>();
+    const int r = threadIdx.x & 127;
+    const uint32_t laneOff = (uint32_t)((warp & 3) * 32) << 16;
+    for (int j = 0; j < w.nmax; j++) {
+#pragma unroll
+      for (int t = 0; t < NT; t++) {
+        if (j >= w.nblk[t]) continue;
+        wait_bar(bar(kBarScaleFull + t), j & 1, wc, 4);
+        const float scale = ctl->scale[t][r];
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kBarScaleEmpty + t));
+        if (j > 0) {
+          wait_bar(bar(kBarPvDone + t), (j - 1) & 1, wc, 5);
+          ptx::tc_fence_after();
+          if (__any_sync(0xffffffffu, scale != 1.f)) {
+            const uint32_t tO = tmem + laneOff + (uint32_t)(C::kOCol0 + t * HDP);
+#pragma unroll
+            for (int ch = 0; ch < HDP / 32; ch++) {
+              uint32_t o[32];
+              ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+              ptx::tmem_st_32x32b_x32(tO + ch * 32, o);
+            }
+            ptx::tmem_wait_st();
+          }
+          ptx::tc_fence_before();
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kBarPvReady + t));
+      }
+    }
+    // epilogue: O / rowsum -> 16-bit -> global
+    const int gp = 1 << p.packShift;
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+      const int n = w.nblk[t];
+      if (n == 0) continue;
+      wait_bar(bar(kBarScaleFull + t), n & 1, wc, 6);
+      const float l = ctl->scale[t][r];
+      wait_bar(bar(kBarPvDone + t), (n - 1) & 1, wc, 7);
+      ptx::tc_fence_after();
+      const float inv = (l > 0.f) ? (1.f / l) : 0.f;
+      const int qpos = w.qlo[t] + (r >> p.packShift);
+      const int head = (w.unit << p.packShift) + (r & (gp - 1));
+      const bool valid = qpos < w.sq;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.O) +
+                                            ((w.qRow0 + qpos) * p.headsQ + head) * (long long)p.headDim);
+      const uint32_t tO = tmem + laneOff + (uint32_t)(C::kOCol0 + t * HDP);
+#pragma unroll
+      for (int ch = 0; ch < HDP / 32; ch++) {
+        uint32_t o[32];
+        ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
+        ptx::tmem_wait_ld();
+        if (valid && ch * 32 < p.headDim) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint4 q;
+            q.x = pack2<kBf16>(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+            q.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+            q.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+            q.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+            dst[ch * 4 + g] = q;
+          }
+        }
+      }
+    }
+  } else {
+    ptx::setmaxnreg_dec<56>();
+    if (warp == 12 && lane == 0) {
+      // ============================================================== MMA issue
+      const int fmt = kBf16 ? 1 : 0;
+      const uint32_t idQK = ptx::instr_desc_f16(fmt, kBlockM, kBlockN, 0, 0);
+      const uint32_t idPV = ptx::instr_desc_f16(fmt, kBlockM, p.pvSplit ? 64 : HDP, 0, 1);
+      // K-major operands (Q, K): rows of 128 bytes, 8-row groups 1024 bytes apart.
+      const uint64_t descK = ptx::smem_desc_sw128(16, 1024);
+      // MN-major operand (V, head dim contiguous): 64-wide slabs kTileBytes/kSub apart, 8-key groups 1024 bytes apart.
+      const uint64_t descV = ptx::smem_desc_sw128(kSubTileBytes, 1024);
+
+      auto issueQK = [&](int t, uint32_t kAddr) {
+        const uint32_t qAddr = sQ + t * C::kTileBytes;
+        const uint32_t d = tmem + (uint32_t)(t * 128);
+#pragma unroll
+        for (int kk = 0; kk < HDP / 16; kk++) {
+          const uint32_t off = (uint32_t)((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+          ptx::mma_ss(d, ptx::smem_desc_at(descK, qAddr + off), ptx::smem_desc_at(descK, kAddr + off), idQK,
+                      kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issuePV = [&](int t, uint32_t vAddr, bool first) {
+        const uint32_t aP = tmem + (uint32_t)(t * 128);
+        const uint32_t d = tmem + (uint32_t)(C::kOCol0 + t * HDP);
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; kk++) {
+          const uint32_t acc = (first && kk == 0) ? 0u : 1u;
+          if (p.pvSplit) {
+#pragma unroll
+            for (int a = 0; a < C::kSub; a++) {
+              ptx::mma_ts(d + a * 64, aP + kk * 8, ptx::smem_desc_at(descV, vAddr + a * kSubTileBytes + kk * 2048),
+                          idPV, acc);
+            }
+          } else {
+            ptx::mma_ts(d, aP + kk * 8, ptx::smem_desc_at(descV, vAddr + kk * 2048), idPV, acc);
+          }
+        }
+      };
+
+      int ld = 0;  // index of the next KV-ring load to consume (K0, V0, K1, V1, ...)
+      // prologue: S_t = Q_t . K_0^T
+      {
+        const int s = ld % NS;
+        wait_bar(bar(kBarKvFull + s), (ld / NS) & 1, wc, 8);
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+          if (w.nblk[t] == 0) continue;
+          wait_bar(bar(kBarQFull + t), 0, wc, 9);
+          ptx::tc_fence_after();
+          issueQK(t, sKV + s * C::kTileBytes);
+          ptx::tc_commit(bar(kBarSFull + t));
+        }
+        ptx::tc_commit(bar(kBarKvEmpty + s));
+        ld++;
+      }
+      for (int j = 0; j < w.nmax; j++) {
+        const int sV = ld % NS;
+        wait_bar(bar(kBarKvFull + sV), (ld / NS) & 1, wc, 10);
+        ld++;
+        const bool hasNext = (j + 1 < w.nmax);
+        const int sK = ld % NS;
+        bool kWaited = false;
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+          if (j >= w.nblk[t]) continue;
+          wait_bar(bar(kBarPvReady + t), j & 1, wc, 11);
+          ptx::tc_fence_after();
+          issuePV(t, sKV + sV * C::kTileBytes, j == 0);
+          ptx::tc_commit(bar(kBarPvDone + t));
+          if (j + 1 < w.nblk[t]) {
+            if (!kWaited) {
+              wait_bar(bar(kBarKvFull + sK), (ld / NS) & 1, wc, 12);
+              ptx::tc_fence_after();
+              kWaited = true;
+            }
+            issueQK(t, sKV + sK * C::kTileBytes);
+            ptx::tc_commit(bar(kBarSFull + t));
+          }
+        }
+        ptx::tc_commit(bar(kBarKvEmpty + sV));
+        if (hasNext) {
+          if (!kWaited) wait_bar(bar(kBarKvFull + sK), (ld / NS) & 1, wc, 13);
+          ptx::tc_commit(bar(kBarKvEmpty + sK));
+          ld++;
+        }
+      }
+    } else if (warp == 13 && lane == 0) {
+      // ============================================================== TMA loads
+      const int gp = 1 << p.packShift;
+#pragma unroll
+      for (int t = 0; t < NT; t++) {
+        if (w.nblk[t] == 0) continue;
+        ptx::mbar_arrive_expect_tx(bar(kBarQFull + t), C::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < C::kSub; a++) {
+          ptx::tma_load_3d(sQ + t * C::kTileBytes + a * kSubTileBytes, &tmQ, bar(kBarQFull + t), a * 64,
+                           w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
+        }
+      }
+      const int numLoads = 2 * w.nmax;  // K0 V0 K1 V1 ...
+      for (int i = 0; i < numLoads; i++) {
+        const int s = i % NS;
+        if (i >= NS) wait_bar(bar(kBarKvEmpty + s), ((i / NS) - 1) & 1, wc, 14);
+        ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
+        const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
+        const int row = (int)(w.kvRow0 + (long long)(i >> 1) * kBlockN);
+#pragma unroll
+        for (int a = 0; a < C::kSub; a++) {
+          ptx::tma_load_3d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+}  // namespace tc
+}  // namespace tfa_b200

@@ -1,0 +1,110 @@
+// Host launcher for one (padded head dim, dtype) instantiation of the tcgen05 attention kernel.
+// Compiled once per pair with -DTFA_HDP=<64|128|192|256> -DTFA_BF16=<0|1> so that the instantiations
+// build in parallel (the reference splits its instantiations the same way, one translation unit per
+// dtype and architecture: reference csrc/flash_attn/kernels/tfa_fwd_*_sm8x.cu).
+//
+// Takes the place of the reference's host launcher (reference csrc/flash_attn/launcher.cuh:28-99):
+// it derives the grid from the problem sizes, opts in to large dynamic shared memory and launches on
+// the caller's stream; in addition it encodes the three TMA descriptors the kernel needs.
+#include <cstdio>
+#include <mutex>
+
+#include "fwd_tc.cuh"
+
+#ifndef TFA_HDP
+#error "compile with -DTFA_HDP=<64|128|192|256>"
+#endif
+#ifndef TFA_BF16
+#error "compile with -DTFA_BF16=<0|1>"
+#endif
+
+namespace tfa_b200 {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_tiled();  // c_abi.cu
+int* device_status_word(int device);  // c_abi.cu: per-device status word (device memory)
+int next_epoch();                     // c_abi.cu
+
+#define TFA_CAT3(a, b, c) a##b##c
+#define TFA_NAME(hdp, bf) TFA_CAT3(launch_fwd_tc_hdp##hdp, _bf, bf)
+#define TFA_NAME2(hdp, bf) TFA_NAME(hdp, bf)
+
+// rows x heads x headDim tensor, 16-bit elements; box = 64 elements x boxHeads x boxRows, 128-byte swizzle.
+static int make_map(CUtensorMap* m, const void* base, long long rows, int heads, int headDim, int boxHeads,
+                    int boxRows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return kCudaError;
+  cuuint64_t dims[3] = {(cuuint64_t)headDim, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)headDim * 2, (cuuint64_t)heads * headDim * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)boxHeads, (cuuint32_t)boxRows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, TFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error_string("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld heads=%d headDim=%d box=%d,%d)",
+                     (int)r, rows, heads, headDim, boxHeads, boxRows);
+    return kCudaError;
+  }
+  return kOk;
+}
+
+int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift, int pvSplit) {
+  using C = tc::Cfg<TFA_HDP>;
+  auto kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0)>;
+
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return kCudaError;
+  static std::once_flag once[64];
+  static cudaError_t attrErr[64];
+  if (device < 0 || device >= 64) return kBadArgument;
+  std::call_once(once[device], [&] {
+    attrErr[device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  });
+  if (attrErr[device] != cudaSuccess) {
+    set_error_string("cudaFuncSetAttribute(%d bytes): %s", C::kSmemBytes, cudaGetErrorString(attrErr[device]));
+    return kCudaError;
+  }
+
+  const int gp = 1 << packShift;
+  const int rowsPerTile = tc::kBlockM >> packShift;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc;
+  if ((rc = make_map(&tmQ, pr.Q, pr.totalQ, pr.headsQ, pr.headDim, gp, rowsPerTile)) != kOk) return rc;
+  if ((rc = make_map(&tmK, pr.K, pr.totalKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
+  if ((rc = make_map(&tmV, pr.V, pr.totalKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
+
+  TcParams p;
+  p.O = pr.O;
+  p.cuQ = pr.cuQ;
+  p.cuKV = pr.cuKV;
+  p.seqLenQ = pr.seqLenQ;
+  p.seqLenKV = pr.seqLenKV;
+  p.headsQ = pr.headsQ;
+  p.headsKV = pr.headsKV;
+  p.headDim = pr.headDim;
+  p.group = pr.headsQ / pr.headsKV;
+  p.packShift = packShift;
+  const int seqPerCta = C::kNT * rowsPerTile;
+  p.numPairs = (pr.seqLenQ + seqPerCta - 1) / seqPerCta;
+  p.causal = pr.causal;
+  p.pvSplit = pvSplit;
+  p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)pr.headDim));
+  p.status = device_status_word(device);
+  p.epoch = next_epoch();
+  if (p.status == nullptr) return kCudaError;
+
+  dim3 grid((unsigned)p.numPairs, (unsigned)(pr.headsQ / gp), (unsigned)pr.batch);
+  kernel<<<grid, tc::kThreads, C::kSmemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error_string("kernel launch failed: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  return kOk;
+}
+
+}  // namespace tfa_b200
