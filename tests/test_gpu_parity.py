@@ -1,0 +1,362 @@
+"""Parity of the CUDA path (through the C ABI) with the oracle, on a B200.  Run with -m gpu."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import tinyfa_b200 as tf
+from oracle import attention_oracle as ao
+from tinyfa_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _ref_tol_ok(ref, test, dtype):
+    """The reference suite's criterion: |ref - test| <= abs + rel * |ref| (tests/cpp/test_flash_attn.cu:112-139)."""
+    rel, ab = cases.REF_TOL[dtype]
+    bad = np.abs(ref - test) > ab + rel * np.abs(ref)
+    return int(bad.sum())
+
+
+def _fixed_inputs(dims, seed=42):
+    B, Sq, Skv, Hq, Hkv, D = dims
+    rng = np.random.default_rng(seed)
+    Q = rng.uniform(-1, 1, (B, Sq, Hq, D)).astype(np.float32)
+    K = rng.uniform(-1, 1, (B, Skv, Hkv, D)).astype(np.float32)
+    V = rng.uniform(-1, 1, (B, Skv, Hkv, D)).astype(np.float32)
+    return Q, K, V
+
+
+def _check_fixed(dims, causal, dtype):
+    Q, K, V = _fixed_inputs(dims)
+    # like the reference test: oracle on the fp32 values, inputs cast afterwards (test_flash_attn.cu:213-225)
+    ref32 = ao.fixed(Q, K, V, causal, "f32")
+    Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+    O = tf.flash_attn_forward(Qd, Kd, Vd, is_causal=causal)
+    out = O.float().cpu().numpy()
+    assert O.shape == Qd.shape and O.dtype == Qd.dtype and O.is_contiguous()
+    assert not np.isnan(out).any()
+    assert _ref_tol_ok(ref32, out, dtype) == 0
+    # tighter: fp64 oracle on exactly the values the kernel saw
+    ref64 = ao.fixed(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), causal, "f64")
+    assert np.abs(out - ref64).max() <= cases.MAXABS_TOL[dtype]
+
+
+def _varlen_inputs(sq, skv, Hq, Hkv, D, seed=42):
+    rng = np.random.default_rng(seed)
+    cu_q = np.concatenate([[0], np.cumsum(sq)]).astype(np.int32)
+    cu_kv = np.concatenate([[0], np.cumsum(skv)]).astype(np.int32)
+    Q = rng.uniform(-1, 1, (int(cu_q[-1]), Hq, D)).astype(np.float32)
+    K = rng.uniform(-1, 1, (int(cu_kv[-1]), Hkv, D)).astype(np.float32)
+    V = rng.uniform(-1, 1, (int(cu_kv[-1]), Hkv, D)).astype(np.float32)
+    return Q, K, V, cu_q, cu_kv
+
+
+def _check_varlen(sq, skv, Hq, Hkv, D, causal, dtype):
+    Q, K, V, cu_q, cu_kv = _varlen_inputs(sq, skv, Hq, Hkv, D)
+    ref32 = ao.varlen(Q, K, V, cu_q, cu_kv, causal, "f32")
+    Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+    cq, ck = torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_kv).cuda()
+    O = tf.flash_attn_varlen_forward(Qd, Kd, Vd, cq, ck, max(sq), max(skv), is_causal=causal)
+    out = O.float().cpu().numpy()
+    assert not np.isnan(out).any()
+    assert _ref_tol_ok(ref32, out, dtype) == 0
+    ref64 = ao.varlen(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), cu_q, cu_kv, causal,
+                      "f64")
+    assert np.abs(out - ref64).max() <= cases.MAXABS_TOL[dtype]
+
+
+# ------------------------------------------------------------------ the reference's 180 cases
+@pytest.mark.parametrize("name", sorted(cases.FIXED_PLAIN))
+def test_reference_suite_fixed_fp32(name):
+    *dims, causal = cases.FIXED_PLAIN[name]
+    _check_fixed(tuple(dims), causal, "fp32")
+
+
+@pytest.mark.parametrize("name", sorted(cases.VARLEN_PLAIN))
+def test_reference_suite_varlen_fp32(name):
+    sq, skv, Hq, Hkv, D, causal = cases.VARLEN_PLAIN[name]
+    _check_varlen(sq, skv, Hq, Hkv, D, causal, "fp32")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("name", sorted(cases.SUITE_FIXED))
+def test_reference_suite_typed_fixed(name, dtype):
+    *dims, causal = cases.SUITE_FIXED[name]
+    _check_fixed(tuple(dims), causal, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("name", sorted(cases.SUITE_VARLEN))
+def test_reference_suite_typed_varlen(name, dtype):
+    sq, skv, Hq, Hkv, D, causal = cases.SUITE_VARLEN[name]
+    _check_varlen(sq, skv, Hq, Hkv, D, causal, dtype)
+
+
+# the un-prefixed cases also on the tensor-core path (the reference runs them in one dtype per build)
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("name", sorted(cases.FIXED_PLAIN))
+def test_reference_suite_fixed_16bit(name, dtype):
+    *dims, causal = cases.FIXED_PLAIN[name]
+    _check_fixed(tuple(dims), causal, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("name", sorted(cases.VARLEN_PLAIN))
+def test_reference_suite_varlen_16bit(name, dtype):
+    sq, skv, Hq, Hkv, D, causal = cases.VARLEN_PLAIN[name]
+    _check_varlen(sq, skv, Hq, Hkv, D, causal, dtype)
+
+
+# ------------------------------------------------------------------ golden vectors of the reference CPU code
+def test_golden_vectors_on_gpu():
+    import json
+    import os
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(here, "golden"))
+    from make_golden import inputs_fixed, inputs_varlen
+
+    gold = np.load(os.path.join(here, "golden", "ref_cpu_golden.npz"))
+    for c in json.load(open(os.path.join(here, "golden", "ref_cpu_golden.json"))):
+        if c["kind"] == "fixed":
+            Q, K, V = inputs_fixed(c["seed"], tuple(c["dims"]))
+            O = tf.flash_attn_forward(*(torch.from_numpy(x).cuda() for x in (Q, K, V)), is_causal=c["causal"])
+        else:
+            Q, K, V, cu_q, cu_kv = inputs_varlen(c["seed"], c["sq"], c["skv"], c["Hq"], c["Hkv"], c["D"])
+            O = tf.flash_attn_varlen_forward(*(torch.from_numpy(x).cuda() for x in (Q, K, V, cu_q, cu_kv)),
+                                             max(c["sq"]), max(c["skv"]), is_causal=c["causal"])
+        assert np.abs(O.cpu().numpy() - gold[c["name"]]).max() <= 1e-4, c["name"]
+
+
+# ------------------------------------------------------------------ benchmark configurations
+def _randn(shape, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g).to(dtype).cuda()
+
+
+def _torch_f64_attention(Q, K, V, causal, head_chunk=4):
+    """fp64 softmax(QK^T/sqrt(d))V on the GPU with plain torch ops, a checker for shapes the CPU oracle
+    cannot finish in seconds.  Q [B,Sq,Hq,D], K/V [B,Skv,Hkv,D]; top-left causal."""
+    B, Sq, Hq, D = Q.shape
+    Skv, Hkv = K.shape[1], K.shape[2]
+    group = Hq // Hkv
+    out = torch.empty(Q.shape, dtype=torch.float64, device=Q.device)
+    mask = None
+    if causal:
+        mask = torch.arange(Skv, device=Q.device)[None, :] > torch.arange(Sq, device=Q.device)[:, None]
+    for b in range(B):
+        for h in range(Hq):
+            q = Q[b, :, h].double()
+            k = K[b, :, h // group].double()
+            v = V[b, :, h // group].double()
+            s = (q @ k.T) / (D ** 0.5)
+            if mask is not None:
+                s.masked_fill_(mask, float("-inf"))
+            out[b, :, h] = torch.softmax(s, dim=-1) @ v
+    return out
+
+
+def test_config1_fp32_small():
+    """fp32, B1 S128 H4 D64, N(0,1) seed 0: max-abs <= 1e-4 against fp64 computed on the host CPU."""
+    Q, K, V = (_randn((1, 128, 4, 64), s, torch.float32) for s in (0, 1, 2))
+    O = tf.flash_attn_forward(Q, K, V)
+    ref = ao.fixed(Q.cpu().numpy(), K.cpu().numpy(), V.cpu().numpy(), False, "f64")
+    assert np.abs(O.cpu().numpy() - ref).max() <= 1e-4
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_config2_full_size(dtype, causal):
+    """B2 S4096 H32 D128: full-size check against fp64 (torch, on the GPU), against the CPU oracle on the first
+    rows, against the reference kernels when they were built, plus size-independent properties."""
+    Q, K, V = (_randn((2, 4096, 32, 128), s, DT[dtype]) for s in (0, 1, 2))
+    O = tf.flash_attn_forward(Q, K, V, is_causal=causal)
+    ref = _torch_f64_attention(Q, K, V, causal)
+    err = (O.double() - ref).abs().max().item()
+    assert err <= 2e-2
+    rows = 64
+    cpu = ao.fixed(Q.float().cpu().numpy(), K.float().cpu().numpy(), V.float().cpu().numpy(), causal, "f64", q_rows=rows)
+    assert np.abs(O[:, :rows].float().cpu().numpy() - cpu[:, :rows]).max() <= 2e-2
+    if ao.ref_gpu_available():
+        ref_err = (ao.ref_gpu_fixed(Q, K, V, causal).double() - ref).abs().max().item()
+        assert err <= 1.5 * ref_err + 5e-4  # no worse than the reference's own error
+    # property: V = 1 gives exactly-normalised rows
+    ones = torch.ones_like(V)
+    O1 = tf.flash_attn_forward(Q, K, ones, is_causal=causal)
+    assert (O1.float() - 1).abs().max().item() <= 1e-2
+    if causal:
+        # property: rows before position p do not depend on keys/values at or after p - bit for bit
+        p = 2500
+        K2, V2 = K.clone(), V.clone()
+        K2[:, p:] = 3.0
+        V2[:, p:] = -7.0
+        O2 = tf.flash_attn_forward(Q, K2, V2, is_causal=True)
+        assert torch.equal(O2[:, :p], O[:, :p])
+    else:
+        # property: permuting the keys (with their values) leaves the result unchanged up to rounding
+        perm = torch.randperm(4096, generator=torch.Generator().manual_seed(5)).cuda()
+        Op = tf.flash_attn_forward(Q, K[:, perm].contiguous(), V[:, perm].contiguous())
+        assert (Op.float() - O.float()).abs().max().item() <= 2e-2
+
+
+def test_config3_gqa_causal_bf16():
+    """bf16 causal GQA B4 S8192 Hq32 Hkv8 D128, checked per batch entry against fp64 torch."""
+    Q = _randn((4, 8192, 32, 128), 0, torch.bfloat16)
+    K = _randn((4, 8192, 8, 128), 1, torch.bfloat16)
+    V = _randn((4, 8192, 8, 128), 2, torch.bfloat16)
+    O = tf.flash_attn_forward(Q, K, V, is_causal=True)
+    for b in (0, 3):
+        ref = _torch_f64_attention(Q[b:b + 1], K[b:b + 1], V[b:b + 1], True)
+        assert (O[b:b + 1].double() - ref).abs().max().item() <= 2e-2
+
+
+def test_config4_varlen_gqa_causal_bf16():
+    """16 packed sequences, lengths U[128, 8192] from a seed, Hq32 Hkv8 D128, int32 cu_seqlens."""
+    rng = np.random.default_rng(0)
+    lens = [int(x) for x in rng.integers(128, 8193, 16)]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    total = int(cu[-1])
+    Q = _randn((total, 32, 128), 0, torch.bfloat16)
+    K = _randn((total, 8, 128), 1, torch.bfloat16)
+    V = _randn((total, 8, 128), 2, torch.bfloat16)
+    cud = torch.from_numpy(cu).cuda()
+    O = tf.flash_attn_varlen_forward(Q, K, V, cud, cud, max(lens), max(lens), is_causal=True)
+    order = np.argsort(lens)
+    for i in (order[0], order[7], order[-1]):  # shortest, a middle one, longest
+        a, b = int(cu[i]), int(cu[i + 1])
+        ref = _torch_f64_attention(Q[None, a:b], K[None, a:b], V[None, a:b], True)
+        assert (O[None, a:b].double() - ref).abs().max().item() <= 2e-2
+    # every sequence equals the fixed-length call on that sequence alone
+    i = int(order[3])
+    a, b = int(cu[i]), int(cu[i + 1])
+    alone = tf.flash_attn_forward(Q[None, a:b].contiguous(), K[None, a:b].contiguous(), V[None, a:b].contiguous(), True)
+    assert (alone[0].float() - O[a:b].float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("hd", [32, 64, 96, 192, 256])
+def test_config5a_headdim_sweep_fp16_causal(hd):
+    Q, K, V = (_randn((8, 2048, 16, hd), s, torch.float16) for s in (0, 1, 2))
+    O = tf.flash_attn_forward(Q, K, V, is_causal=True)
+    for b in (0, 7):
+        ref = _torch_f64_attention(Q[b:b + 1], K[b:b + 1], V[b:b + 1], True)
+        assert (O[b:b + 1].double() - ref).abs().max().item() <= 2e-2
+
+
+def test_config5b_decode_shape_bf16():
+    """B64 Sq1 Skv32768 Hq32 Hkv8 D128 non-causal (2^31 K elements: 64-bit addressing)."""
+    Q = _randn((64, 1, 32, 128), 0, torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    K = torch.randn(64, 32768, 8, 128, generator=g, device="cuda", dtype=torch.bfloat16)
+    V = torch.randn(64, 32768, 8, 128, generator=g, device="cuda", dtype=torch.bfloat16)
+    O = tf.flash_attn_forward(Q, K, V)
+    for b in (0, 31, 63):
+        ref = _torch_f64_attention(Q[b:b + 1], K[b:b + 1], V[b:b + 1], False)
+        assert (O[b:b + 1].double() - ref).abs().max().item() <= 2e-2
+
+
+# ------------------------------------------------------------------ boundary behaviour
+def test_python_argument_checks_on_gpu():
+    q = torch.zeros(2, 8, 4, 64, dtype=torch.float16, device="cuda")
+    k = torch.zeros(2, 8, 2, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="contiguous"):
+        tf.flash_attn_forward(q.transpose(1, 2), k, k)
+    with pytest.raises(RuntimeError, match="4D"):
+        tf.flash_attn_forward(q[0], k, k)
+    with pytest.raises(RuntimeError, match="same dtype"):
+        tf.flash_attn_forward(q, k.float(), k)
+    with pytest.raises(RuntimeError, match="Batch sizes"):
+        tf.flash_attn_forward(q, k[:1], k[:1])
+    with pytest.raises(RuntimeError, match="same seqlen"):
+        tf.flash_attn_forward(q, k, k[:, :4].contiguous())
+    with pytest.raises(RuntimeError, match="Head dims"):
+        tf.flash_attn_forward(q, k[..., :32].contiguous(), k[..., :32].contiguous())
+    with pytest.raises(RuntimeError, match="divisible"):
+        tf.flash_attn_forward(q[:, :, :3].contiguous(), k, k)
+    with pytest.raises(RuntimeError, match="only supports"):
+        tf.flash_attn_forward(q.double(), k.double(), k.double())
+    with pytest.raises(RuntimeError, match="BAD_HEAD_DIM"):
+        z = torch.zeros(1, 4, 2, 80, dtype=torch.float16, device="cuda")
+        tf.flash_attn_forward(z, z, z)
+    cu = torch.tensor([0, 8, 16], dtype=torch.int32, device="cuda")
+    q3, k3 = q.reshape(16, 4, 64), k.reshape(16, 2, 64)
+    with pytest.raises(RuntimeError, match="int32"):
+        tf.flash_attn_varlen_forward(q3, k3, k3, cu.long(), cu, 8, 8)
+    with pytest.raises(RuntimeError, match="3D"):
+        tf.flash_attn_varlen_forward(q, k3, k3, cu, cu, 8, 8)
+    with pytest.raises(RuntimeError, match="1D"):
+        tf.flash_attn_varlen_forward(q3, k3, k3, cu[None], cu[None], 8, 8)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "fp32"])
+def test_c_abi_raw_pointers_stream_and_untouched_rows(dtype):
+    """Direct C-ABI calls: non-default stream, output rows of key-less sequences stay untouched, no stray
+    stores outside O (guard bands), totals read from the device when the caller passes -1."""
+    lib = _lib.load()
+    Hq, Hkv, D = 4, 2, 64
+    sq, skv = [5, 70, 9], [33, 0, 140]
+    Q, K, V, cu_q, cu_kv = _varlen_inputs(sq, skv, Hq, Hkv, D, seed=3)
+    Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+    cq, ck = torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_kv).cuda()
+    guard = 4096
+    buf = torch.full((Qd.numel() + 2 * guard,), 77.0, dtype=DT[dtype], device="cuda")
+    O = buf[guard:guard + Qd.numel()].view_as(Qd)
+    stream = torch.cuda.Stream()
+    code = {"fp16": 1, "fp32": 3}[dtype]
+    with torch.cuda.stream(stream):
+        rc = lib.tfa_b200_fwd_varlen(Qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), O.data_ptr(), cq.data_ptr(),
+                                     ck.data_ptr(), code, 3, max(sq), max(skv), -1, -1, Hq, Hkv, D, 1,
+                                     stream.cuda_stream)
+    assert rc == 0, _lib.last_error()
+    stream.synchronize()
+    assert torch.all(buf[:guard] == 77.0) and torch.all(buf[-guard:] == 77.0)
+    assert torch.all(O[5:75] == 77.0)  # the sequence without keys is left alone
+    ref = ao.varlen(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), cu_q, cu_kv, True)
+    out = O.float().cpu().numpy()
+    keep = np.r_[0:5, 75:84]
+    assert np.abs(out[keep] - ref[keep]).max() <= cases.MAXABS_TOL[dtype]
+    # the Python mirror returns zeros for those rows, as the reference binding does
+    Op = tf.flash_attn_varlen_forward(Qd, Kd, Vd, cq, ck, max(sq), max(skv), is_causal=True)
+    assert torch.all(Op[5:75] == 0)
+
+
+def test_fixed_len_guard_bands_partial_tiles():
+    """Odd sizes on the tensor-core path: nothing is written outside O."""
+    for dims in [(2, 67, 83, 4, 2, 128), (1, 1, 300, 8, 1, 64), (3, 129, 129, 2, 2, 96)]:
+        B, Sq, Skv, Hq, Hkv, D = dims
+        Q, K, V = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in _fixed_inputs(dims, seed=9))
+        guard = 8192
+        buf = torch.full((Q.numel() + 2 * guard,), 55.0, dtype=torch.bfloat16, device="cuda")
+        O = buf[guard:guard + Q.numel()].view_as(Q)
+        rc = _lib.load().tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), 2, B, Sq, Skv, Hq, Hkv,
+                                      D, 1, None)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        assert torch.all(buf[:guard] == 55.0) and torch.all(buf[-guard:] == 55.0)
+        ref = ao.fixed(Q.float().cpu().numpy(), K.float().cpu().numpy(), V.float().cpu().numpy(), True)
+        assert np.abs(O.float().cpu().numpy() - ref).max() <= 2e-2
+
+
+@pytest.mark.parametrize("pack", [0, 1])
+def test_gqa_packing_modes_agree(pack):
+    """Interleaving a KV group's Q heads into one tile is a scheduling choice, not a numerical one."""
+    dims = (2, 200, 333, 8, 2, 128)
+    Q, K, V = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in _fixed_inputs(dims, seed=11))
+    tf.set_option("pack_gqa", pack)
+    try:
+        O = tf.flash_attn_forward(Q, K, V, is_causal=True)
+    finally:
+        tf.set_option("pack_gqa", -1)
+    ref = ao.fixed(Q.float().cpu().numpy(), K.float().cpu().numpy(), V.float().cpu().numpy(), True)
+    assert np.abs(O.float().cpu().numpy() - ref).max() <= 2e-2
+
+
+def test_no_bounded_wait_gave_up():
+    """Runs last in this file: every kernel launched above finished through its normal path."""
+    site = ctypes.c_int(0)
+    assert _lib.load().tfa_b200_device_status(ctypes.byref(site)) == 0, site.value
