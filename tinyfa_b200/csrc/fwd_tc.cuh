@@ -56,6 +56,7 @@ namespace tc {
 constexpr int kBlockM = 128;  // query rows per tile = TMEM lanes
 constexpr int kBlockN = 128;  // keys per KV block
 constexpr int kThreads = 512;
+constexpr float kRescaleLog2 = 8.0f;  // lazy-rescale threshold, log2 units
 constexpr int kSubTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 16-bit elements), one swizzle-128B slab
 
 template <int HDP>
@@ -73,13 +74,14 @@ struct Cfg {
 enum Bar : int {
   kBarQFull = 0,      // [2]  Q tile landed
   kBarSFull = 2,      // [2]  S = Q.K^T finished (tcgen05.commit)
-  kBarPvReady = 4,    // [2]  P written (4 softmax warps) and O rescaled (4 correction warps)
+  kBarP0Ready = 4,    // [2]  first half of P written (4 softmax warps) and O rescaled (4 correction warps)
   kBarPvDone = 6,     // [2]  O += P.V finished (tcgen05.commit)
   kBarScaleFull = 8,  // [2]  softmax published the rescale factor (or the final row sum)
   kBarScaleEmpty = 10,  // [2] correction consumed it
-  kBarKvFull = 12,    // [kStages]
-  kBarKvEmpty = 20,   // [kStages]
-  kNumBars = 28,
+  kBarP1Ready = 12,   // [2]  second half of P written (4 softmax warps)
+  kBarKvFull = 14,    // [kStages]
+  kBarKvEmpty = 22,   // [kStages]
+  kNumBars = 30,
 };
 
 struct Ctl {
@@ -120,6 +122,35 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// two-wide fp32 FMA / ADD on a register pair
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)),
+        "l"(reinterpret_cast<const uint64_t&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
 }
 
 template <bool kBf16>
@@ -212,7 +243,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int t = 0; t < 2; t++) {
       ptx::mbar_init(bar(kBarQFull + t), 1);
       ptx::mbar_init(bar(kBarSFull + t), 1);
-      ptx::mbar_init(bar(kBarPvReady + t), 8);
+      ptx::mbar_init(bar(kBarP0Ready + t), 8);
+      ptx::mbar_init(bar(kBarP1Ready + t), 4);
       ptx::mbar_init(bar(kBarPvDone + t), 1);
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
       ptx::mbar_init(bar(kBarScaleEmpty + t), 4);
@@ -272,15 +304,28 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
           }
         }
-        float mx = -INFINITY;
+        // row max: four independent chains of 3-input max
+        float mx4[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
+          mx4[q] = fmaxf(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
 #pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[q][i]));
+          for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
         }
-        const float mNew = fmaxf(m, mx);
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // Lazy rescale: keep the old reference max while the new one exceeds it by less than kRescaleLog2 in
+        // the exp2 domain (P then grows up to 2^kRescaleLog2, harmless in fp32 sums and 16-bit P); the
+        // result is unchanged because O and the row sum stay relative to the same reference value.
+        float mNew = fmaxf(m, mx);
+        float scale = 1.f;
+        if (m == -INFINITY) {
+          scale = 0.f;  // first block (or nothing visible yet): nothing accumulated to rescale
+        } else if ((mNew - m) * c > kRescaleLog2) {
+          scale = ex2((m - mNew) * c);
+        } else {
+          mNew = m;
+        }
         const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
-        const float scale = (m == -INFINITY) ? 0.f : ex2((m - mUse) * c);
         m = mNew;
 
         // hand the rescale factor to the correction warps before the long exp loop
@@ -289,26 +334,32 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
 
-        const float negMc = -mUse * c;
-        float sum = 0.f;
-        uint32_t pk[2][32];
+        const float2 c2 = make_float2(c, c);
+        const float2 negMc2 = make_float2(-mUse * c, -mUse * c);
+        float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
+        for (int half = 0; half < 2; half++) {
+          uint32_t pk[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(v[q][i]), c, negMc));
-            const float p1 = ex2(fmaf(__uint_as_float(v[q][i + 1]), c, negMc));
-            sum += p0 + p1;
-            pk[q >> 1][(q & 1) * 16 + (i >> 1)] = pack2<kBf16>(p0, p1);
+          for (int qq = 0; qq < 2; qq++) {
+            const int q = half * 2 + qq;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float2 x = make_float2(__uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
+              x = ffma2(x, c2, negMc2);
+              x.x = ex2(x.x);
+              x.y = ex2(x.y);
+              sum2 = fadd2(sum2, x);
+              pk[qq * 16 + (i >> 1)] = pack2<kBf16>(x.x, x.y);
+            }
           }
+          ptx::tmem_st_32x32b_x32(tS + half * 32, pk);
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + t));
         }
-        l = l * scale + sum;
-        ptx::tmem_st_32x32b_x32(tS, pk[0]);
-        ptx::tmem_st_32x32b_x32(tS + 32, pk[1]);
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kBarPvReady + t));
+        l = l * scale + (sum2.x + sum2.y);
       }
       // final row sum for the epilogue
       wait_bar(bar(kBarScaleEmpty + t), (n - 1) & 1, wc, 3);
@@ -348,7 +399,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tc_fence_before();
         }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kBarPvReady + t));
+        if (lane == 0) ptx::mbar_arrive(bar(kBarP0Ready + t));
       }
     }
     // epilogue: O / rowsum -> 16-bit -> global
@@ -408,11 +459,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                       kk > 0 ? 1u : 0u);
         }
       };
-      auto issuePV = [&](int t, uint32_t vAddr, bool first) {
+      auto issuePV = [&](int t, uint32_t vAddr, bool first, int half) {
         const uint32_t aP = tmem + (uint32_t)(t * 128);
         const uint32_t d = tmem + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; kk++) {
+        for (int k4 = 0; k4 < kBlockN / 32; k4++) {
+          const int kk = half * (kBlockN / 32) + k4;
           const uint32_t acc = (first && kk == 0) ? 0u : 1u;
           if (p.pvSplit) {
 #pragma unroll
@@ -452,9 +504,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int t = 0; t < NT; t++) {
           if (j >= w.nblk[t]) continue;
-          wait_bar(bar(kBarPvReady + t), j & 1, wc, 11);
+          wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
           ptx::tc_fence_after();
-          issuePV(t, sKV + sV * C::kTileBytes, j == 0);
+          issuePV(t, sKV + sV * C::kTileBytes, j == 0, 0);
+          wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
+          ptx::tc_fence_after();
+          issuePV(t, sKV + sV * C::kTileBytes, j == 0, 1);
           ptx::tc_commit(bar(kBarPvDone + t));
           if (j + 1 < w.nblk[t]) {
             if (!kWaited) {
