@@ -13,7 +13,7 @@
 // CTA = 16 warps:
 //   warps 0-3   softmax for Q tile 0 (one thread per query row, 128 rows)
 //   warps 4-7   softmax for Q tile 1 (when the CTA owns two Q tiles)
-//   warps 8-11  correction: rescales O in tensor memory when the running max moves, final 1/sum, stores O
+//   warps 8-11  epilogue: final 1/rowsum, conversion to the 16-bit type, stores O
 //   warp  12    issues every tcgen05.mma (one thread)
 //   warp  13    issues every TMA load (one thread)
 //   warps 14-15 idle (they exist so that the last warpgroup can give its registers away)
@@ -74,15 +74,29 @@ struct Cfg {
 enum Bar : int {
   kBarQFull = 0,      // [2]  Q tile landed
   kBarSFull = 2,      // [2]  S = Q.K^T finished (tcgen05.commit)
-  kBarP0Ready = 4,    // [2]  first half of P written (4 softmax warps) and O rescaled (4 correction warps)
+  kBarP0Ready = 4,    // [2]  first half of P written (4 softmax warps; O already rescaled if it had to be)
   kBarPvDone = 6,     // [2]  O += P.V finished (tcgen05.commit)
-  kBarScaleFull = 8,  // [2]  softmax published the rescale factor (or the final row sum)
-  kBarScaleEmpty = 10,  // [2] correction consumed it
+  kBarScaleFull = 8,  // [2]  softmax published the final row sums (once per tile)
+  kBarUnused = 10,    // [2]
   kBarP1Ready = 12,   // [2]  second half of P written (4 softmax warps)
   kBarKvFull = 14,    // [kStages]
   kBarKvEmpty = 22,   // [kStages]
   kNumBars = 30,
 };
+
+// Optional timeline instrumentation (debug builds only, -DTFA_TRACE): one CTA records clock64() at named points.
+#ifdef TFA_TRACE
+constexpr int kTraceRoles = 5, kTraceIters = 64, kTracePts = 8;
+__device__ unsigned long long g_trace[kTraceRoles * kTraceIters * kTracePts];
+#define TFA_TR(role, iter, pt)                                                                      \
+  do {                                                                                              \
+    if (traceOn && (iter) < kTraceIters) g_trace[((role) * kTraceIters + (iter)) * kTracePts + (pt)] = clock64(); \
+  } while (0)
+#else
+#define TFA_TR(role, iter, pt) \
+  do {                         \
+  } while (0)
+#endif
 
 struct Ctl {
   uint64_t bars[kNumBars];
@@ -243,11 +257,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int t = 0; t < 2; t++) {
       ptx::mbar_init(bar(kBarQFull + t), 1);
       ptx::mbar_init(bar(kBarSFull + t), 1);
-      ptx::mbar_init(bar(kBarP0Ready + t), 8);
+      ptx::mbar_init(bar(kBarP0Ready + t), 4);
       ptx::mbar_init(bar(kBarP1Ready + t), 4);
       ptx::mbar_init(bar(kBarPvDone + t), 1);
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
-      ptx::mbar_init(bar(kBarScaleEmpty + t), 4);
     }
     for (int s = 0; s < NS; s++) {
       ptx::mbar_init(bar(kBarKvFull + s), 1);
@@ -271,6 +284,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmemBase;
   const WaitCtx wc{&ctl->failed, p.status, p.epoch};
+#ifdef TFA_TRACE
+  const bool traceOn = (blockIdx.x == gridDim.x / 2) && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+#endif
 
   if (warp < 8) {
     // ================================================================ softmax
@@ -286,10 +302,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int j = 0; j < n; j++) {
         wait_bar(bar(kBarSFull + t), j & 1, wc, 1);
         ptx::tc_fence_after();
+        if ((warp & 3) == 0) TFA_TR(t, j, 0);
         uint32_t v[4][32];
 #pragma unroll
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
+        if ((warp & 3) == 0) TFA_TR(t, j, 1);
 
         const int kbase = j * kBlockN;
         const bool needMask = (kbase + kBlockN > w.skv) || (p.causal && (kbase + kBlockN - 1 > w.qlo[t]));
@@ -313,26 +331,36 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if ((warp & 3) == 0) TFA_TR(t, j, 2);
         // Lazy rescale: keep the old reference max while the new one exceeds it by less than kRescaleLog2 in
         // the exp2 domain (P then grows up to 2^kRescaleLog2, harmless in fp32 sums and 16-bit P); the
         // result is unchanged because O and the row sum stay relative to the same reference value.
         float mNew = fmaxf(m, mx);
-        float scale = 1.f;
-        if (m == -INFINITY) {
-          scale = 0.f;  // first block (or nothing visible yet): nothing accumulated to rescale
-        } else if ((mNew - m) * c > kRescaleLog2) {
-          scale = ex2((m - mNew) * c);
-        } else {
-          mNew = m;
+        const bool grow = (m != -INFINITY) && ((mNew - m) * c > kRescaleLog2);
+        if (__any_sync(0xffffffffu, grow)) {
+          // Rare: some row of this warp moves its reference max.  Rescale that row's O in tensor memory (rows
+          // that keep their max multiply by 1) once the previous P.V has landed; P.V of this block waits for
+          // the P0 arrival below, so it sees the rescaled accumulator.
+          const float scale = grow ? ex2((m - mNew) * c) : 1.f;
+          wait_bar(bar(kBarPvDone + t), (j - 1) & 1, wc, 5);
+          ptx::tc_fence_after();
+          const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
+#pragma unroll 1
+          for (int ch = 0; ch < HDP / 32; ch++) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+            ptx::tmem_st_32x32b_x32(tO + ch * 32, o);
+          }
+          ptx::tmem_wait_st();
+          l *= scale;
         }
+        if (m != -INFINITY && !grow) mNew = m;
         const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
         m = mNew;
-
-        // hand the rescale factor to the correction warps before the long exp loop
-        if (j > 0) wait_bar(bar(kBarScaleEmpty + t), (j - 1) & 1, wc, 2);
-        ctl->scale[t][r] = scale;
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
+        if ((warp & 3) == 0) TFA_TR(t, j, 3);
 
         const float2 c2 = make_float2(c, c);
         const float2 negMc2 = make_float2(-mUse * c, -mUse * c);
@@ -353,62 +381,33 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               pk[qq * 16 + (i >> 1)] = pack2<kBf16>(x.x, x.y);
             }
           }
+          if ((warp & 3) == 0) TFA_TR(t, j, 4 + 2 * half);
           ptx::tmem_st_32x32b_x32(tS + half * 32, pk);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + t));
+          if ((warp & 3) == 0) TFA_TR(t, j, 5 + 2 * half);
         }
-        l = l * scale + (sum2.x + sum2.y);
+        l += sum2.x + sum2.y;
       }
       // final row sum for the epilogue
-      wait_bar(bar(kBarScaleEmpty + t), (n - 1) & 1, wc, 3);
       ctl->scale[t][r] = l;
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
     }
   } else if (warp < 12) {
-    // ================================================================ correction + epilogue
+    // ================================================================ epilogue
     ptx::setmaxnreg_dec<88>();
     const int r = threadIdx.x & 127;
     const uint32_t laneOff = (uint32_t)((warp & 3) * 32) << 16;
-    for (int j = 0; j < w.nmax; j++) {
-#pragma unroll
-      for (int t = 0; t < NT; t++) {
-        if (j >= w.nblk[t]) continue;
-        wait_bar(bar(kBarScaleFull + t), j & 1, wc, 4);
-        const float scale = ctl->scale[t][r];
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kBarScaleEmpty + t));
-        if (j > 0) {
-          wait_bar(bar(kBarPvDone + t), (j - 1) & 1, wc, 5);
-          ptx::tc_fence_after();
-          if (__any_sync(0xffffffffu, scale != 1.f)) {
-            const uint32_t tO = tmem + laneOff + (uint32_t)(C::kOCol0 + t * HDP);
-#pragma unroll
-            for (int ch = 0; ch < HDP / 32; ch++) {
-              uint32_t o[32];
-              ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
-              ptx::tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
-              ptx::tmem_st_32x32b_x32(tO + ch * 32, o);
-            }
-            ptx::tmem_wait_st();
-          }
-          ptx::tc_fence_before();
-        }
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar(kBarP0Ready + t));
-      }
-    }
     // epilogue: O / rowsum -> 16-bit -> global
     const int gp = 1 << p.packShift;
 #pragma unroll
     for (int t = 0; t < NT; t++) {
       const int n = w.nblk[t];
       if (n == 0) continue;
-      wait_bar(bar(kBarScaleFull + t), n & 1, wc, 6);
+      wait_bar(bar(kBarScaleFull + t), 0, wc, 6);
       const float l = ctl->scale[t][r];
       wait_bar(bar(kBarPvDone + t), (n - 1) & 1, wc, 7);
       ptx::tc_fence_after();
@@ -449,19 +448,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // MN-major operand (V, head dim contiguous): 64-wide slabs kTileBytes/kSub apart, 8-key groups 1024 bytes apart.
       const uint64_t descV = ptx::smem_desc_sw128(kSubTileBytes, 1024);
 
+      const uint32_t kHi = (uint32_t)(descK >> 32), vHi = (uint32_t)(descV >> 32);
+      const uint32_t kLoT = (uint32_t)descK, vLoT = (uint32_t)descV;  // LBO field; start address added below
       auto issueQK = [&](int t, uint32_t kAddr) {
-        const uint32_t qAddr = sQ + t * C::kTileBytes;
+        const uint32_t qLo = kLoT | ((sQ + t * C::kTileBytes) >> 4);
+        const uint32_t kLo = kLoT | (kAddr >> 4);
         const uint32_t d = tmem + (uint32_t)(t * 128);
 #pragma unroll
         for (int kk = 0; kk < HDP / 16; kk++) {
-          const uint32_t off = (uint32_t)((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
-          ptx::mma_ss(d, ptx::smem_desc_at(descK, qAddr + off), ptx::smem_desc_at(descK, kAddr + off), idQK,
-                      kk > 0 ? 1u : 0u);
+          const uint32_t off = (uint32_t)((kk >> 2) * kSubTileBytes + (kk & 3) * 32) >> 4;
+          ptx::mma_ss_lohi(d, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
         }
       };
       auto issuePV = [&](int t, uint32_t vAddr, bool first, int half) {
         const uint32_t aP = tmem + (uint32_t)(t * 128);
         const uint32_t d = tmem + (uint32_t)(C::kOCol0 + t * HDP);
+        const uint32_t vLo = vLoT | (vAddr >> 4);
 #pragma unroll
         for (int k4 = 0; k4 < kBlockN / 32; k4++) {
           const int kk = half * (kBlockN / 32) + k4;
@@ -469,11 +471,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (p.pvSplit) {
 #pragma unroll
             for (int a = 0; a < C::kSub; a++) {
-              ptx::mma_ts(d + a * 64, aP + kk * 8, ptx::smem_desc_at(descV, vAddr + a * kSubTileBytes + kk * 2048),
-                          idPV, acc);
+              ptx::mma_ts_lohi(d + a * 64, aP + kk * 8, vLo + ((a * kSubTileBytes + kk * 2048) >> 4), vHi, idPV, acc);
             }
           } else {
-            ptx::mma_ts(d, aP + kk * 8, ptx::smem_desc_at(descV, vAddr + kk * 2048), idPV, acc);
+            ptx::mma_ts_lohi(d, aP + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, acc);
           }
         }
       };
@@ -506,11 +507,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (j >= w.nblk[t]) continue;
           wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
           ptx::tc_fence_after();
+          TFA_TR(3, j, t * 4 + 0);
           issuePV(t, sKV + sV * C::kTileBytes, j == 0, 0);
           wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
           ptx::tc_fence_after();
+          TFA_TR(3, j, t * 4 + 1);
           issuePV(t, sKV + sV * C::kTileBytes, j == 0, 1);
           ptx::tc_commit(bar(kBarPvDone + t));
+          TFA_TR(3, j, t * 4 + 2);
           if (j + 1 < w.nblk[t]) {
             if (!kWaited) {
               wait_bar(bar(kBarKvFull + sK), (ld / NS) & 1, wc, 12);
@@ -519,6 +523,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             issueQK(t, sKV + sK * C::kTileBytes);
             ptx::tc_commit(bar(kBarSFull + t));
+            TFA_TR(3, j, t * 4 + 3);
           }
         }
         ptx::tc_commit(bar(kBarKvEmpty + sV));
@@ -545,6 +550,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int i = 0; i < numLoads; i++) {
         const int s = i % NS;
         if (i >= NS) wait_bar(bar(kBarKvEmpty + s), ((i / NS) - 1) & 1, wc, 14);
+        TFA_TR(4, i >> 1, (i & 1) * 2);
         ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
         const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
         const int row = (int)(w.kvRow0 + (long long)(i >> 1) * kBlockN);

@@ -107,4 +107,15 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift, int pvSpli
   return kOk;
 }
 
+#ifdef TFA_TRACE
+// debug builds only: copy the timeline of the instrumented CTA to the host
+extern "C" int tfa_b200_debug_read_trace(unsigned long long* host, int count) {
+  const int n = tc::kTraceRoles * tc::kTraceIters * tc::kTracePts;
+  if (count < n) return -1;
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(host, tc::g_trace, sizeof(unsigned long long) * n) != cudaSuccess) return -2;
+  return n;
+}
+#endif
+
 }  // namespace tfa_b200

@@ -140,6 +140,36 @@ __device__ __forceinline__ void mma_ts(uint32_t dTmem, uint32_t aTmem, uint64_t 
       : "memory");
 }
 
+// Same two instructions with the 64-bit shared-memory descriptors passed as (lo, hi) words, so that stepping a
+// descriptor through a tile is a single 32-bit add on the lo word (start address field, 16-byte units).
+__device__ __forceinline__ void mma_ss_lohi(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
+                                            uint32_t iDesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n" ::"r"(dTmem),
+      "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lohi(uint32_t dTmem, uint32_t aTmem, uint32_t bLo, uint32_t bHi, uint32_t iDesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n" ::"r"(dTmem),
+      "r"(aTmem), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives TMEM lane (base lane + i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
