@@ -14,9 +14,10 @@
 //   warps 0-3   softmax for Q tile 0 (one thread per query row, 128 rows)
 //   warps 4-7   softmax for Q tile 1 (when the CTA owns two Q tiles)
 //   warps 8-11  epilogue: final 1/rowsum, conversion to the 16-bit type, stores O
-//   warp  12    issues every tcgen05.mma (one thread)
+//   warp  12    issues the tcgen05.mma of Q tile 0 (one thread)
 //   warp  13    issues every TMA load (one thread)
-//   warps 14-15 idle (they exist so that the last warpgroup can give its registers away)
+//   warp  14    issues the tcgen05.mma of Q tile 1 (one thread)
+//   warp  15    idle
 //
 // Tensor memory columns (fp32 words per lane; lane = query row of the tile):
 //   [t*128, t*128+128)            S of Q tile t; the 16-bit P overwrites the first 64 columns
@@ -77,7 +78,7 @@ enum Bar : int {
   kBarP0Ready = 4,    // [2]  first half of P written (4 softmax warps; O already rescaled if it had to be)
   kBarPvDone = 6,     // [2]  O += P.V finished (tcgen05.commit)
   kBarScaleFull = 8,  // [2]  softmax published the final row sums (once per tile)
-  kBarUnused = 10,    // [2]
+  kBarTurn = 10,      // [2]  issue-turn token of the MMA thread of tile t
   kBarP1Ready = 12,   // [2]  second half of P written (4 softmax warps)
   kBarKvFull = 14,    // [kStages]
   kBarKvEmpty = 22,   // [kStages]
@@ -259,12 +260,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::mbar_init(bar(kBarSFull + t), 1);
       ptx::mbar_init(bar(kBarP0Ready + t), 4);
       ptx::mbar_init(bar(kBarP1Ready + t), 4);
+      ptx::mbar_init(bar(kBarTurn + t), 1);
       ptx::mbar_init(bar(kBarPvDone + t), 1);
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
     }
     for (int s = 0; s < NS; s++) {
       ptx::mbar_init(bar(kBarKvFull + s), 1);
-      ptx::mbar_init(bar(kBarKvEmpty + s), 1);
+      ptx::mbar_init(bar(kBarKvEmpty + s), 2);  // one arrival per MMA-issuing thread
     }
     ctl->failed = 0;
     ptx::fence_barrier_init();
@@ -388,6 +390,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + t));
           if ((warp & 3) == 0) TFA_TR(t, j, 5 + 2 * half);
+          if (t == 0 && (warp & 3) != 0 && half == 0) TFA_TR(2, j, 2 + (warp & 3));
+          if (t == 0 && (warp & 3) != 0 && (warp & 3) < 3 && half == 1) TFA_TR(2, j, 5 + (warp & 3));
         }
         l += sum2.x + sum2.y;
       }
@@ -438,7 +442,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
   } else {
     ptx::setmaxnreg_dec<56>();
-    if (warp == 12 && lane == 0) {
+    if ((warp == 12 || warp == 14) && lane == 0) {
       // ============================================================== MMA issue
       const int fmt = kBf16 ? 1 : 0;
       const uint32_t idQK = ptx::instr_desc_f16(fmt, kBlockM, kBlockN, 0, 0);
@@ -479,34 +483,72 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       };
 
-      int ld = 0;  // index of the next KV-ring load to consume (K0, V0, K1, V1, ...)
-      // prologue: S_t = Q_t . K_0^T
+      // One issuing thread per Q tile (warp 12: tile 0, warp 14: tile 1).  Every wait and commit costs the issuing
+      // thread ~100 clocks during which it feeds nothing to the tensor pipe; with two issuers the other tile's MMAs
+      // fill those gaps.  Both threads walk the same K0 V0 K1 V1 ... ring; a stage is released by one arrival per
+      // issuer (a tcgen05.commit when the tile used the block, a plain arrive when it did not).
+      const int t = (warp - 12) >> 1;
+      const int n = (t < NT) ? w.nblk[t] : 0;
+      // A thread that does not use a block still waits for it to land before releasing it: that keeps its
+      // arrivals in step with the loader, so two arrivals of one thread can never complete a phase on their own.
+      auto release = [&](int stage, uint32_t phase, bool used) {
+        if (used) {
+          ptx::tc_commit(bar(kBarKvEmpty + stage));
+        } else {
+          wait_bar(bar(kBarKvFull + stage), phase, wc, 13);
+          ptx::mbar_arrive(bar(kBarKvEmpty + stage));
+        }
+      };
+      // The two issuers take strict turns (A: tile 0, B: tile 1, A, B, ...), which keeps the two tiles in
+      // anti-phase: one tile's softmax runs while the other tile's MMAs run.  Without the turn token the two
+      // tiles drift into lock-step and share both the MUFU and the tensor pipe at the same time.  Turn k of A
+      // needs turn k-1 of B, turn k of B needs turn k of A; a thread does its data waits before asking for the
+      // token and releases ring stages after passing it on, so those latencies overlap the other thread's issue.
+      const bool dual = (NT == 2) && w.nblk[0] > 0 && w.nblk[1] > 0;
+      const uint32_t myTurn = bar(kBarTurn + t), otherTurn = bar(kBarTurn + (t ^ 1));
+      auto takeTurn = [&](int k) {
+        if (!dual) return;
+        if (t == 0) {
+          if (k > 0) wait_bar(myTurn, (k - 1) & 1, wc, 16);
+        } else {
+          wait_bar(myTurn, k & 1, wc, 17);
+        }
+      };
+      auto passTurn = [&]() {
+        if (dual) ptx::mbar_arrive(otherTurn);
+      };
+      int ld = 0;  // index of the next KV-ring load to consume
       {
-        const int s = ld % NS;
-        wait_bar(bar(kBarKvFull + s), (ld / NS) & 1, wc, 8);
-#pragma unroll
-        for (int t = 0; t < NT; t++) {
-          if (w.nblk[t] == 0) continue;
+        const int s0 = ld % NS;
+        if (n > 0) {
+          wait_bar(bar(kBarKvFull + s0), (ld / NS) & 1, wc, 8);
           wait_bar(bar(kBarQFull + t), 0, wc, 9);
           ptx::tc_fence_after();
-          issueQK(t, sKV + s * C::kTileBytes);
+        }
+        takeTurn(0);
+        if (n > 0) {
+          issueQK(t, sKV + s0 * C::kTileBytes);
           ptx::tc_commit(bar(kBarSFull + t));
         }
-        ptx::tc_commit(bar(kBarKvEmpty + s));
+        passTurn();
+        release(s0, 0, n > 0);
         ld++;
       }
       for (int j = 0; j < w.nmax; j++) {
         const int sV = ld % NS;
-        wait_bar(bar(kBarKvFull + sV), (ld / NS) & 1, wc, 10);
+        const uint32_t phV = (ld / NS) & 1;
         ld++;
         const bool hasNext = (j + 1 < w.nmax);
         const int sK = ld % NS;
-        bool kWaited = false;
-#pragma unroll
-        for (int t = 0; t < NT; t++) {
-          if (j >= w.nblk[t]) continue;
+        const uint32_t phK = (ld / NS) & 1;
+        if (j < n) {
+          wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
+          if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
           wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
           ptx::tc_fence_after();
+        }
+        takeTurn(j + 1);
+        if (j < n) {
           TFA_TR(3, j, t * 4 + 0);
           issuePV(t, sKV + sV * C::kTileBytes, j == 0, 0);
           wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
@@ -515,21 +557,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           issuePV(t, sKV + sV * C::kTileBytes, j == 0, 1);
           ptx::tc_commit(bar(kBarPvDone + t));
           TFA_TR(3, j, t * 4 + 2);
-          if (j + 1 < w.nblk[t]) {
-            if (!kWaited) {
-              wait_bar(bar(kBarKvFull + sK), (ld / NS) & 1, wc, 12);
-              ptx::tc_fence_after();
-              kWaited = true;
-            }
+          if (j + 1 < n) {
             issueQK(t, sKV + sK * C::kTileBytes);
             ptx::tc_commit(bar(kBarSFull + t));
             TFA_TR(3, j, t * 4 + 3);
           }
         }
-        ptx::tc_commit(bar(kBarKvEmpty + sV));
+        passTurn();
+        release(sV, phV, j < n);
         if (hasNext) {
-          if (!kWaited) wait_bar(bar(kBarKvFull + sK), (ld / NS) & 1, wc, 13);
-          ptx::tc_commit(bar(kBarKvEmpty + sK));
+          release(sK, phK, j + 1 < n);
           ld++;
         }
       }
