@@ -72,7 +72,6 @@ int tfa_b200_device_status(int* site);
 /*
  * Tuning / debugging knobs (process-wide).  No counterpart in the reference, whose tile table is fixed
  * at compile time (csrc/flash_attn/config.cuh:133-272).
- *   "pv_split"  0/1  issue P.V as one MMA per 64-wide head-dim slice (1) or one MMA for the whole head dim (0)
  *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto / never / always
  * Returns TFA_B200_BAD_ARGUMENT for an unknown name.
  */

@@ -56,7 +56,7 @@ def test_status_codes_for_bad_arguments():
     assert v(p, p, p, p, None, None, 1, 2, 16, 16, 32, 32, 4, 4, 64, 0, None) == 3  # null cu_seqlens
     assert v(p, p, p, p, p, p, 1, 0, 16, 16, 0, 0, 4, 4, 64, 0, None) == 0
     assert lib.tfa_b200_set_option(b"no_such_option", 1) == 3
-    assert lib.tfa_b200_set_option(b"pv_split", 0) == 0
+    assert lib.tfa_b200_set_option(b"pack_gqa", -1) == 0
 
 
 def test_python_mirror_rejects_like_the_reference_binding():

@@ -20,14 +20,14 @@
 namespace tfa_b200 {
 
 // ---- instantiations (fwd_tc_inst.cu, one object per pair)
-int launch_fwd_tc_hdp64_bf0(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp64_bf1(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp128_bf0(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp128_bf1(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp192_bf0(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp192_bf1(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp256_bf0(const FwdProblem&, int, int);
-int launch_fwd_tc_hdp256_bf1(const FwdProblem&, int, int);
+int launch_fwd_tc_hdp64_bf0(const FwdProblem&, int);
+int launch_fwd_tc_hdp64_bf1(const FwdProblem&, int);
+int launch_fwd_tc_hdp128_bf0(const FwdProblem&, int);
+int launch_fwd_tc_hdp128_bf1(const FwdProblem&, int);
+int launch_fwd_tc_hdp192_bf0(const FwdProblem&, int);
+int launch_fwd_tc_hdp192_bf1(const FwdProblem&, int);
+int launch_fwd_tc_hdp256_bf0(const FwdProblem&, int);
+int launch_fwd_tc_hdp256_bf1(const FwdProblem&, int);
 
 static thread_local char g_err[512] = "";
 
@@ -38,7 +38,6 @@ void set_error_string(const char* fmt, ...) {
   va_end(ap);
 }
 
-static std::atomic<int> g_optPvSplit{0};
 static std::atomic<int> g_optPackGqa{-1};
 static std::atomic<int> g_epoch{1};
 
@@ -122,18 +121,17 @@ static int dispatch(const FwdProblem& p) {
   if (p.dtype == kFp32) return launch_fwd_fp32(p);
   const bool bf = (p.dtype == kBf16);
   const int ps = pick_pack_shift(p);
-  const int split = g_optPvSplit.load();
   switch (p.headDim) {
     case 32:
     case 64:
-      return bf ? launch_fwd_tc_hdp64_bf1(p, ps, split) : launch_fwd_tc_hdp64_bf0(p, ps, split);
+      return bf ? launch_fwd_tc_hdp64_bf1(p, ps) : launch_fwd_tc_hdp64_bf0(p, ps);
     case 96:
     case 128:
-      return bf ? launch_fwd_tc_hdp128_bf1(p, ps, split) : launch_fwd_tc_hdp128_bf0(p, ps, split);
+      return bf ? launch_fwd_tc_hdp128_bf1(p, ps) : launch_fwd_tc_hdp128_bf0(p, ps);
     case 192:
-      return bf ? launch_fwd_tc_hdp192_bf1(p, ps, split) : launch_fwd_tc_hdp192_bf0(p, ps, split);
+      return bf ? launch_fwd_tc_hdp192_bf1(p, ps) : launch_fwd_tc_hdp192_bf0(p, ps);
     case 256:
-      return bf ? launch_fwd_tc_hdp256_bf1(p, ps, split) : launch_fwd_tc_hdp256_bf0(p, ps, split);
+      return bf ? launch_fwd_tc_hdp256_bf1(p, ps) : launch_fwd_tc_hdp256_bf0(p, ps);
     default:
       return kBadHeadDim;
   }
@@ -287,10 +285,6 @@ extern "C" int tfa_b200_device_status(int* site) {
 
 extern "C" int tfa_b200_set_option(const char* name, int value) {
   if (name == nullptr) return kBadArgument;
-  if (strcmp(name, "pv_split") == 0) {
-    g_optPvSplit.store(value ? 1 : 0);
-    return kOk;
-  }
   if (strcmp(name, "pack_gqa") == 0) {
     g_optPackGqa.store(value < 0 ? -1 : (value ? 1 : 0));
     return kOk;

@@ -16,8 +16,8 @@
 //   warps 8-11  epilogue: final 1/rowsum, conversion to the 16-bit type, stores O
 //   warp  12    issues the tcgen05.mma of Q tile 0 (one thread)
 //   warp  13    issues every TMA load (one thread)
-//   warp  14    issues the tcgen05.mma of Q tile 1 (one thread)
-//   warp  15    idle
+//   warp  14    idle
+//   warp  15    issues the tcgen05.mma of Q tile 1 (one thread)
 //
 // Tensor memory columns (fp32 words per lane; lane = query row of the tile):
 //   [t*128, t*128+128)            S of Q tile t; the 16-bit P overwrites the first 64 columns
@@ -46,7 +46,6 @@ struct TcParams {
   int packShift;  // log2 of the number of Q heads interleaved into one 128-row tile
   int numPairs;   // gridDim.x
   int causal;
-  int pvSplit;    // debug knob: 1 = issue P.V as one MMA per 64-wide slice of the head dim
   float scaleLog2;  // log2(e) / sqrt(headDim)
   int* status;      // device status word
   int epoch;        // launch epoch (24 bits)
@@ -57,6 +56,15 @@ namespace tc {
 constexpr int kBlockM = 128;  // query rows per tile = TMEM lanes
 constexpr int kBlockN = 128;  // keys per KV block
 constexpr int kThreads = 512;
+#ifndef TFA_ISSUER_B
+#define TFA_ISSUER_B 15
+#endif
+constexpr int kIssuerB = TFA_ISSUER_B;  // warp that issues the MMAs of Q tile 1
+#ifndef TFA_EMU_COUNT
+#define TFA_EMU_COUNT 1
+#endif
+constexpr int kEmuPeriod = 8;              // of every kEmuPeriod pairs of exponentials ...
+constexpr int kEmuCount = TFA_EMU_COUNT;   // ... this many are evaluated on the FMA pipe instead of the MUFU
 constexpr float kRescaleLog2 = 8.0f;  // lazy-rescale threshold, log2 units
 constexpr int kSubTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 16-bit elements), one swizzle-128B slab
 
@@ -166,6 +174,33 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
       : "=l"(reinterpret_cast<uint64_t&>(d))
       : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
   return d;
+}
+
+__device__ __forceinline__ float2 fadd2_rm(float2 a, float2 b) {  // round toward -inf
+  float2 d;
+  asm("add.rm.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
+}
+
+// exp2 on the FMA pipe for a pair of values (the MUFU unit is the co-bottleneck of this kernel: 16 ex2/clk/SM
+// against 128x128 exponentials per tile-block).  x = floor(x) + f; 2^f by a cubic with p(0) = 1 (max relative
+// error 8.6e-5, below the rounding of the 16-bit P it feeds); 2^floor(x) by adding to the exponent field.
+// The magic constant 1.5*2^23 makes the low mantissa bits of t hold floor(x); x is clamped at -127.
+__device__ __forceinline__ float2 ex2_fma2(float2 x) {
+  const float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -127.f);
+  x.y = fmaxf(x.y, -127.f);
+  const float2 t = fadd2_rm(x, make_float2(kMagic, kMagic));
+  const float2 xi = fadd2(t, make_float2(-kMagic, -kMagic));
+  const float2 f = ffma2(xi, make_float2(-1.f, -1.f), x);
+  float2 p = ffma2(make_float2(0.07706704f, 0.07706704f), f, make_float2(0.22764499f, 0.22764499f));
+  p = ffma2(p, f, make_float2(0.69511679f, 0.69511679f));
+  p = ffma2(p, f, make_float2(1.f, 1.f));
+  p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return p;
 }
 
 template <bool kBf16>
@@ -292,7 +327,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (warp < 8) {
     // ================================================================ softmax
-    ptx::setmaxnreg_inc<184>();
+    ptx::setmaxnreg_inc<176>();
     const int t = warp >> 2;
     if (t < NT && w.nblk[t] > 0) {
       const int r = threadIdx.x & 127;
@@ -377,8 +412,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int i = 0; i < 32; i += 2) {
               float2 x = make_float2(__uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
               x = ffma2(x, c2, negMc2);
-              x.x = ex2(x.x);
-              x.y = ex2(x.y);
+              if (((i >> 1) % kEmuPeriod) < kEmuCount) {  // compile-time pattern: this pair goes to the FMA pipe
+                x = ex2_fma2(x);
+              } else {
+                x.x = ex2(x.x);
+                x.y = ex2(x.y);
+              }
               sum2 = fadd2(sum2, x);
               pk[qq * 16 + (i >> 1)] = pack2<kBf16>(x.x, x.y);
             }
@@ -402,7 +441,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
   } else if (warp < 12) {
     // ================================================================ epilogue
-    ptx::setmaxnreg_dec<88>();
+    ptx::setmaxnreg_dec<96>();
     const int r = threadIdx.x & 127;
     const uint32_t laneOff = (uint32_t)((warp & 3) * 32) << 16;
     // epilogue: O / rowsum -> 16-bit -> global
@@ -441,12 +480,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else {
-    ptx::setmaxnreg_dec<56>();
-    if ((warp == 12 || warp == 14) && lane == 0) {
+    ptx::setmaxnreg_dec<64>();
+    if ((warp == 12 || warp == kIssuerB) && lane == 0) {
       // ============================================================== MMA issue
       const int fmt = kBf16 ? 1 : 0;
       const uint32_t idQK = ptx::instr_desc_f16(fmt, kBlockM, kBlockN, 0, 0);
-      const uint32_t idPV = ptx::instr_desc_f16(fmt, kBlockM, p.pvSplit ? 64 : HDP, 0, 1);
+      const uint32_t idPV = ptx::instr_desc_f16(fmt, kBlockM, HDP, 0, 1);
       // K-major operands (Q, K): rows of 128 bytes, 8-row groups 1024 bytes apart.
       const uint64_t descK = ptx::smem_desc_sw128(16, 1024);
       // MN-major operand (V, head dim contiguous): 64-wide slabs kTileBytes/kSub apart, 8-key groups 1024 bytes apart.
@@ -454,32 +493,26 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
       const uint32_t kHi = (uint32_t)(descK >> 32), vHi = (uint32_t)(descV >> 32);
       const uint32_t kLoT = (uint32_t)descK, vLoT = (uint32_t)descV;  // LBO field; start address added below
-      auto issueQK = [&](int t, uint32_t kAddr) {
-        const uint32_t qLo = kLoT | ((sQ + t * C::kTileBytes) >> 4);
+      // Issue helpers.  The tensor pipe overlaps at most one MMA with the issuing thread's next instructions, so
+      // everything between two tcgen05.mma costs tensor time: per MMA there is one 32-bit add on a descriptor word.
+      const uint32_t qLo = kLoT | ((sQ + (uint32_t)(warp != 12) * C::kTileBytes) >> 4);
+      const uint32_t dS = tmem + (uint32_t)((warp != 12) * 128);
+      const uint32_t dO = tmem + (uint32_t)(C::kOCol0 + (warp != 12) * HDP);
+      auto issueQK = [&](uint32_t kAddr, int part) {  // part 0 / 1: first / second half of the k-steps
         const uint32_t kLo = kLoT | (kAddr >> 4);
-        const uint32_t d = tmem + (uint32_t)(t * 128);
 #pragma unroll
-        for (int kk = 0; kk < HDP / 16; kk++) {
+        for (int k2 = 0; k2 < HDP / 32; k2++) {
+          const int kk = part * (HDP / 32) + k2;
           const uint32_t off = (uint32_t)((kk >> 2) * kSubTileBytes + (kk & 3) * 32) >> 4;
-          ptx::mma_ss_lohi(d, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
+          ptx::mma_ss_lohi(dS, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
         }
       };
-      auto issuePV = [&](int t, uint32_t vAddr, bool first, int half) {
-        const uint32_t aP = tmem + (uint32_t)(t * 128);
-        const uint32_t d = tmem + (uint32_t)(C::kOCol0 + t * HDP);
+      auto issuePV = [&](uint32_t vAddr, uint32_t firstAcc, int half) {  // firstAcc: accumulate flag of k-step 0
         const uint32_t vLo = vLoT | (vAddr >> 4);
 #pragma unroll
         for (int k4 = 0; k4 < kBlockN / 32; k4++) {
           const int kk = half * (kBlockN / 32) + k4;
-          const uint32_t acc = (first && kk == 0) ? 0u : 1u;
-          if (p.pvSplit) {
-#pragma unroll
-            for (int a = 0; a < C::kSub; a++) {
-              ptx::mma_ts_lohi(d + a * 64, aP + kk * 8, vLo + ((a * kSubTileBytes + kk * 2048) >> 4), vHi, idPV, acc);
-            }
-          } else {
-            ptx::mma_ts_lohi(d, aP + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, acc);
-          }
+          ptx::mma_ts_lohi(dO, dS + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, kk == 0 ? firstAcc : 1u);
         }
       };
 
@@ -487,7 +520,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // thread ~100 clocks during which it feeds nothing to the tensor pipe; with two issuers the other tile's MMAs
       // fill those gaps.  Both threads walk the same K0 V0 K1 V1 ... ring; a stage is released by one arrival per
       // issuer (a tcgen05.commit when the tile used the block, a plain arrive when it did not).
-      const int t = (warp - 12) >> 1;
+      const int t = (warp != 12) ? 1 : 0;
       const int n = (t < NT) ? w.nblk[t] : 0;
       // A thread that does not use a block still waits for it to land before releasing it: that keeps its
       // arrivals in step with the loader, so two arrivals of one thread can never complete a phase on their own.
@@ -527,7 +560,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         takeTurn(0);
         if (n > 0) {
-          issueQK(t, sKV + s0 * C::kTileBytes);
+          issueQK(sKV + s0 * C::kTileBytes, 0);
+          issueQK(sKV + s0 * C::kTileBytes, 1);
           ptx::tc_commit(bar(kBarSFull + t));
         }
         passTurn();
@@ -541,29 +575,41 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const bool hasNext = (j + 1 < w.nmax);
         const int sK = ld % NS;
         const uint32_t phK = (ld / NS) & 1;
+        bool p1Ready = false;
         if (j < n) {
           wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
           if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
           wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
-          ptx::tc_fence_after();
+          p1Ready = ptx::mbar_try_wait(bar(kBarP1Ready + t), j & 1);
         }
         takeTurn(j + 1);
+        // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
+        // ~150 clocks to see it, and its first MMAs then queue behind the rest of this turn instead of finding
+        // the tensor pipe idle.  MMAs of the two tiles touch disjoint tensor memory, so interleaving is harmless.
         if (j < n) {
-          TFA_TR(3, j, t * 4 + 0);
-          issuePV(t, sKV + sV * C::kTileBytes, j == 0, 0);
-          wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
           ptx::tc_fence_after();
+          TFA_TR(3, j, t * 4 + 0);
+          issuePV(sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
+          if (!p1Ready) {
+            wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
+            ptx::tc_fence_after();
+          }
           TFA_TR(3, j, t * 4 + 1);
-          issuePV(t, sKV + sV * C::kTileBytes, j == 0, 1);
-          ptx::tc_commit(bar(kBarPvDone + t));
+          issuePV(sKV + sV * C::kTileBytes, 1u, 1);
           TFA_TR(3, j, t * 4 + 2);
           if (j + 1 < n) {
-            issueQK(t, sKV + sK * C::kTileBytes);
+            issueQK(sKV + sK * C::kTileBytes, 0);
+            passTurn();
+            issueQK(sKV + sK * C::kTileBytes, 1);
             ptx::tc_commit(bar(kBarSFull + t));
             TFA_TR(3, j, t * 4 + 3);
+          } else {
+            passTurn();
           }
+          ptx::tc_commit(bar(kBarPvDone + t));
+        } else {
+          passTurn();
         }
-        passTurn();
         release(sV, phV, j < n);
         if (hasNext) {
           release(sK, phK, j + 1 < n);

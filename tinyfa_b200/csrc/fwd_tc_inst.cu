@@ -52,7 +52,7 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, int heads,
   return kOk;
 }
 
-int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift, int pvSplit) {
+int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   using C = tc::Cfg<TFA_HDP>;
   auto kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0)>;
 
@@ -91,7 +91,6 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift, int pvSpli
   const int seqPerCta = C::kNT * rowsPerTile;
   p.numPairs = (pr.seqLenQ + seqPerCta - 1) / seqPerCta;
   p.causal = pr.causal;
-  p.pvSplit = pvSplit;
   p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)pr.headDim));
   p.status = device_status_word(device);
   p.epoch = next_epoch();
