@@ -73,6 +73,7 @@ int tfa_b200_device_status(int* site);
  * Tuning / debugging knobs (process-wide).  No counterpart in the reference, whose tile table is fixed
  * at compile time (csrc/flash_attn/config.cuh:133-272).
  *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto / never / always
+ *   "split_kv" -1/0/n  split-KV path for short query blocks (seqQ * group <= 16): auto / never / exactly n splits
  * Returns TFA_B200_BAD_ARGUMENT for an unknown name.
  */
 int tfa_b200_set_option(const char* name, int value);

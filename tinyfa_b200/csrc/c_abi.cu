@@ -29,6 +29,12 @@ int launch_fwd_tc_hdp192_bf1(const FwdProblem&, int);
 int launch_fwd_tc_hdp256_bf0(const FwdProblem&, int);
 int launch_fwd_tc_hdp256_bf1(const FwdProblem&, int);
 
+// ---- split-KV path for short query blocks (fwd_decode.cu)
+bool splitkv_applicable(const FwdProblem& p);
+int splitkv_num_splits(const FwdProblem& p, int numSMs);
+size_t splitkv_scratch_floats(const FwdProblem& p, int splits);
+int launch_fwd_splitkv(const FwdProblem& p, int splits, float* scratch);
+
 static thread_local char g_err[512] = "";
 
 void set_error_string(const char* fmt, ...) {
@@ -39,6 +45,7 @@ void set_error_string(const char* fmt, ...) {
 }
 
 static std::atomic<int> g_optPackGqa{-1};
+static std::atomic<int> g_optSplitKv{-1};  // -1 auto, 0 never, n > 0 force n splits when applicable
 static std::atomic<int> g_epoch{1};
 
 int next_epoch() { return (g_epoch.fetch_add(1) & 0x7FFFFF) + 1; }
@@ -117,8 +124,45 @@ static int pick_pack_shift(const FwdProblem& p) {
   return (p.seqLenQ < 128) ? shift : 0;  // auto: short query blocks share one tile across the group's heads
 }
 
+static int num_sms() {
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
+// Short query blocks: stream K/V once for all Q heads of a KV head and split the key range over CTAs.  The partial
+// results live in a stream-ordered scratch allocation that is released behind the combine kernel.
+static int dispatch_splitkv(const FwdProblem& p, int splits) {
+  const size_t floats = splitkv_scratch_floats(p, splits);
+  float* scratch = nullptr;
+  if (floats > 0) {
+    cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&scratch), floats * sizeof(float), p.stream);
+    if (e != cudaSuccess) {
+      set_error_string("cudaMallocAsync(%zu bytes) for split-KV partials: %s", floats * sizeof(float),
+                       cudaGetErrorString(e));
+      return kCudaError;
+    }
+  }
+  const int rc = launch_fwd_splitkv(p, splits, scratch);
+  if (scratch != nullptr) cudaFreeAsync(scratch, p.stream);
+  return rc;
+}
+
 static int dispatch(const FwdProblem& p) {
   if (p.dtype == kFp32) return launch_fwd_fp32(p);
+  const int optSplit = g_optSplitKv.load();
+  if (optSplit != 0 && p.totalQ >= 0 && splitkv_applicable(p)) {
+    int splits = (optSplit > 0) ? optSplit : splitkv_num_splits(p, num_sms());
+    const int maxSplits = (p.seqLenKV + 63) / 64;
+    if (splits > maxSplits) splits = maxSplits;
+    return dispatch_splitkv(p, splits);
+  }
   const bool bf = (p.dtype == kBf16);
   const int ps = pick_pack_shift(p);
   switch (p.headDim) {
@@ -287,6 +331,10 @@ extern "C" int tfa_b200_set_option(const char* name, int value) {
   if (name == nullptr) return kBadArgument;
   if (strcmp(name, "pack_gqa") == 0) {
     g_optPackGqa.store(value < 0 ? -1 : (value ? 1 : 0));
+    return kOk;
+  }
+  if (strcmp(name, "split_kv") == 0) {
+    g_optSplitKv.store(value < 0 ? -1 : value);
     return kOk;
   }
   set_error_string("unknown option '%s'", name);
