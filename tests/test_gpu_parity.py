@@ -260,6 +260,39 @@ def test_config5b_decode_shape_bf16():
         assert (O[b:b + 1].double() - ref).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("split", [-1, 1, 3, 0])
+@pytest.mark.parametrize("shape", [(2, 1, 700, 8, 2, 128, False), (2, 4, 1000, 8, 2, 128, True), (2, 2, 513, 16, 2, 64, False),
+                                   (1, 1, 2049, 4, 4, 256, False), (1, 3, 777, 5, 1, 128, True)])
+def test_short_query_split_kv_path(shape, split):
+    """Short query blocks go through the split-KV kernel; every split count (and the tensor-core path, 0) agrees with fp64."""
+    *dims, causal = shape
+    Q, K, V = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in _fixed_inputs(tuple(dims), seed=21))
+    tf.set_option("split_kv", split)
+    try:
+        O = tf.flash_attn_forward(Q, K, V, is_causal=causal)
+    finally:
+        tf.set_option("split_kv", -1)
+    ref = ao.fixed(Q.float().cpu().numpy(), K.float().cpu().numpy(), V.float().cpu().numpy(), causal)
+    assert np.abs(O.float().cpu().numpy() - ref).max() <= 2e-2
+
+
+def test_varlen_decode_with_empty_sequence():
+    """Packed single-token queries against ragged key lengths, one sequence without keys (rows stay zero)."""
+    sq, skv = [1, 1, 2, 1, 1], [300, 1500, 77, 0, 4096]
+    Q, K, V, cu_q, cu_kv = _varlen_inputs(sq, skv, 8, 2, 128, seed=5)
+    Qd, Kd, Vd = (torch.from_numpy(x).to(torch.float16).cuda() for x in (Q, K, V))
+    for split in (-1, 1, 4):
+        tf.set_option("split_kv", split)
+        try:
+            O = tf.flash_attn_varlen_forward(Qd, Kd, Vd, torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_kv).cuda(),
+                                             max(sq), max(skv))
+        finally:
+            tf.set_option("split_kv", -1)
+        ref = ao.varlen(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), cu_q, cu_kv, False)
+        assert np.abs(O.float().cpu().numpy() - ref).max() <= 2e-2
+        assert torch.all(O[4] == 0)
+
+
 # ------------------------------------------------------------------ boundary behaviour
 def test_python_argument_checks_on_gpu():
     q = torch.zeros(2, 8, 4, 64, dtype=torch.float16, device="cuda")

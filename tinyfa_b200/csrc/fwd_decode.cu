@@ -142,7 +142,8 @@ __global__ void __launch_bounds__(kThreads) fwd_splitkv_kernel(const Params p) {
     qRow0 = (long long)b * sq;
     kvRow0 = (long long)b * skv;
   }
-  if (sq <= 0 || skv <= 0) return;
+  if (sq <= 0) return;
+  if (skv <= 0 && p.splits == 1) return;  // nothing to write; with splits > 1 the partials must still be defined
   const int nRows = sq * p.group;  // <= 16 by dispatch
   int keyEnd = skv;
   if (p.causal) keyEnd = min(keyEnd, sq);  // top-left causal: key j needs j <= i <= sq-1
