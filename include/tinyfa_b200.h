@@ -80,6 +80,31 @@ int tfa_b200_set_option(const char* name, int value);
 
 const char* tfa_b200_version(void);
 
+/*
+ * Allocation-free decode forward.  No counterpart in the reference (which has neither a split-KV path nor any
+ * scratch memory).  Same tensors, layouts and result as tfa_b200_fwd, restricted to what the split-KV kernel
+ * handles: fp16 / bf16, headDim 64 / 128 / 256, seqLenQ * (numHeadsQ / numHeadsKV) <= 16, seqLenKV >= 256.
+ *
+ * For callers that cannot let a library allocate: engines that hand all device memory to their own planner at
+ * start-up, and decode loops that must not risk a stalling or failing driver allocation.  tfa_b200_fwd keeps the
+ * partial results of its key-range splits in a stream-ordered allocation; this entry point keeps them in a fixed
+ * array inside the library image, TFA_B200_NOALLOC_SCRATCH_FLOATS floats (16 MiB) per GPU that loads the library,
+ * held until the process exits.  It calls no cudaMalloc / cudaFree / allocating routine of any kind.
+ *
+ * numSplits: 0 lets the library choose, n > 0 asks for n key-range splits.  The partials need
+ * numSplits * batchSize * seqLenQ * numHeadsQ * (headDim + 1) floats (none for one split); a call that needs more
+ * than the array holds returns TFA_B200_TOO_LARGE and launches nothing.
+ *
+ * The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before starting any stream capture.  All calls on a device share the one array:
+ * calls whose kernels can overlap on the GPU (different streams without ordering) race on it - serialise them.
+ * The array keeps the last call's partials; nothing in it needs to be zero and nothing stale is ever read.
+ */
+#define TFA_B200_NOALLOC_SCRATCH_FLOATS (4u * 1024u * 1024u)
+int tfa_b200_fwd_decode_noalloc(const void* Q, const void* K, const void* V, void* O, int dtype, int batchSize,
+                                int seqLenQ, int seqLenKV, int numHeadsQ, int numHeadsKV, int headDim, int isCausal,
+                                int numSplits, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

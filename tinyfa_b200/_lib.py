@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "tfa_b200_device_status",
     "tfa_b200_set_option",
     "tfa_b200_version",
+    "tfa_b200_fwd_decode_noalloc",
 )
 
 _lib = None
@@ -57,6 +58,8 @@ def load():
     lib.tfa_b200_device_status.restype = ci
     lib.tfa_b200_set_option.argtypes = [ctypes.c_char_p, ci]
     lib.tfa_b200_set_option.restype = ci
+    lib.tfa_b200_fwd_decode_noalloc.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp]
+    lib.tfa_b200_fwd_decode_noalloc.restype = ci
     lib.tfa_b200_version.argtypes = []
     lib.tfa_b200_version.restype = ctypes.c_char_p
     _lib = lib

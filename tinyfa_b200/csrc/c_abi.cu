@@ -85,7 +85,7 @@ int* device_status_word(int device) {
   return g_statusWord[device];
 }
 
-static int check_device() {
+int check_device() {
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) {
@@ -181,7 +181,7 @@ static int dispatch(const FwdProblem& p) {
   }
 }
 
-static int validate_common(const void* Q, const void* K, const void* V, void* O, int dtype, int batch, int sq, int skv,
+int validate_common(const void* Q, const void* K, const void* V, void* O, int dtype, int batch, int sq, int skv,
                            int hq, int hkv, int d) {
   if (dtype != kFp16 && dtype != kBf16 && dtype != kFp32) {
     set_error_string("unsupported dtype code %d (1 = fp16, 2 = bf16, 3 = fp32)", dtype);

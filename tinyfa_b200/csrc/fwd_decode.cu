@@ -21,6 +21,7 @@
 
 #include <mutex>
 
+#include "../../include/tinyfa_b200.h"
 #include "tfa_common.cuh"
 
 namespace tfa_b200 {
@@ -492,3 +493,95 @@ int launch_fwd_splitkv(const FwdProblem& p, int splits, float* scratch) {
 }
 
 }  // namespace tfa_b200
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the split-KV path.
+//
+// Who needs it: serving processes that give all device memory to their own planner at start-up (a fixed KV-cache
+// budget, nothing left for the driver to hand out later) and latency-critical decode loops in which a driver
+// allocation may stall or fail.  For them the fp32 partial results of the key-range splits live in the fixed array
+// below instead of a stream-ordered allocation.  The price: every GPU that loads this library carries the array
+// (TFA_B200_NOALLOC_SCRATCH_FLOATS floats) until the process exits, and all calls share it.
+namespace tfa_b200 {
+namespace decode {
+
+static __device__ __align__(256) float g_static_scratch[TFA_B200_NOALLOC_SCRATCH_FLOATS];
+
+// Device address of g_static_scratch on the current device.  In host code the symbol's name is only a handle, not
+// a device pointer, so the address is fetched once per device with cudaGetSymbolAddress (that device current).
+static int static_scratch_ptr(float** out) {
+  static std::mutex mutex;
+  static float* cached[64] = {nullptr};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= 64) {
+    set_error_string("cudaGetDevice: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cached[device] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error_string("cudaGetSymbolAddress(static split-KV scratch) on device %d: %s", device, cudaGetErrorString(e));
+      return kCudaError;
+    }
+    cached[device] = static_cast<float*>(p);
+  }
+  *out = cached[device];
+  return kOk;
+}
+
+}  // namespace decode
+}  // namespace tfa_b200
+
+extern "C" int tfa_b200_fwd_decode_noalloc(const void* Q, const void* K, const void* V, void* O, int dtype,
+                                           int batchSize, int seqLenQ, int seqLenKV, int numHeadsQ, int numHeadsKV,
+                                           int headDim, int isCausal, int numSplits, void* stream) {
+  using namespace tfa_b200;
+  int rc = validate_common(Q, K, V, O, dtype, batchSize, seqLenQ, seqLenKV, numHeadsQ, numHeadsKV, headDim);
+  if (rc != kOk) return rc;
+  if (batchSize == 0 || seqLenQ == 0 || seqLenKV == 0) return kOk;
+  if ((rc = check_device()) != kOk) return rc;
+  FwdProblem p;
+  p.Q = Q;
+  p.K = K;
+  p.V = V;
+  p.O = O;
+  p.cuQ = nullptr;
+  p.cuKV = nullptr;
+  p.dtype = dtype;
+  p.batch = batchSize;
+  p.seqLenQ = seqLenQ;
+  p.seqLenKV = seqLenKV;
+  p.totalQ = (long long)batchSize * seqLenQ;
+  p.totalKV = (long long)batchSize * seqLenKV;
+  p.headsQ = numHeadsQ;
+  p.headsKV = numHeadsKV;
+  p.headDim = headDim;
+  p.causal = isCausal ? 1 : 0;
+  p.stream = static_cast<cudaStream_t>(stream);
+  if (!splitkv_applicable(p)) {
+    set_error_string("tfa_b200_fwd_decode_noalloc handles fp16/bf16, headDim 64/128/256, seqLenQ * (Hq/Hkv) <= 16 and "
+                     "seqLenKV >= 256 only (got dtype %d, headDim %d, seqLenQ %d, group %d, seqLenKV %d)",
+                     dtype, headDim, seqLenQ, numHeadsQ / numHeadsKV, seqLenKV);
+    return kBadArgument;
+  }
+  int device = 0, sms = 148;
+  if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  int splits = (numSplits > 0) ? numSplits : splitkv_num_splits(p, sms);
+  const int maxSplits = (seqLenKV + decode::kBlockKeys - 1) / decode::kBlockKeys;
+  if (splits > maxSplits) splits = maxSplits;
+  const size_t need = splitkv_scratch_floats(p, splits);
+  if (need > (size_t)TFA_B200_NOALLOC_SCRATCH_FLOATS) {
+    set_error_string("split-KV partials need %zu floats (%d splits x %lld rows x (%d + 1)) but the built-in scratch holds "
+                     "%zu; use fewer splits or tfa_b200_fwd",
+                     need, splits, (long long)p.totalQ * numHeadsQ, headDim, (size_t)TFA_B200_NOALLOC_SCRATCH_FLOATS);
+    return kTooLarge;
+  }
+  float* scratch = nullptr;
+  if ((rc = decode::static_scratch_ptr(&scratch)) != kOk) return rc;
+  // Every (split, row) partial that the combine kernel reads is written by the split kernel of the same call, so
+  // nothing in the array has to start at zero and contents left by an earlier call are never consumed.
+  return launch_fwd_splitkv(p, splits, need > 0 ? scratch : nullptr);
+}

@@ -55,5 +55,9 @@ struct DeviceStatusWord {
 int launch_fwd_tc(const FwdProblem& p);      // fp16 / bf16: tcgen05 + TMEM + TMA kernel family
 int launch_fwd_fp32(const FwdProblem& p);    // fp32: CUDA-core FMA kernel
 void set_error_string(const char* fmt, ...);
+// argument checks shared by every entry point (c_abi.cu); both return a Status
+int validate_common(const void* Q, const void* K, const void* V, void* O, int dtype, int batch, int sq, int skv, int hq,
+                    int hkv, int d);
+int check_device();  // current device must be compute capability 10.x
 
 }  // namespace tfa_b200
