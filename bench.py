@@ -36,8 +36,18 @@ WORKLOADS = {
     "fp16_noncausal_b2_s4096_h32_d128": ("fp16", False, 2, 4096, 4096, 32, 32, 128),
     "fp16_causal_b2_s4096_h32_d128": ("fp16", True, 2, 4096, 4096, 32, 32, 128),
     "bf16_causal_gqa_b4_s8192_h32_8_d128": ("bf16", True, 4, 8192, 8192, 32, 8, 128),
+    # decode shapes are HBM-bound: reported in GB/s of K+V read once
+    "bf16_decode_b64_skv32768_h32_8_d128": ("bf16", False, 64, 1, 32768, 32, 8, 128),
+    "bf16_decode_b8_skv32768_h32_8_d128": ("bf16", False, 8, 1, 32768, 32, 8, 128),
 }
 DEFAULT_WORKLOAD = "bf16_noncausal_b2_s4096_h32_d128"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+# (decode: batch-8 capture scaled by units processed; traffic grows in proportion to batch).
+NCU_TRAFFIC_BYTES = {
+    "bf16_noncausal_b2_s4096_h32_d128": 201429248 + 49005312,
+    "bf16_decode_b64_skv32768_h32_8_d128": int((1074021000 + 4879104) * 8),
+    "bf16_decode_b8_skv32768_h32_8_d128": 1074021000 + 4879104,
+}
 FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 
 
@@ -106,6 +116,14 @@ def measured_peak():
             return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
     except Exception:
         return FALLBACK_PEAK_TFLOPS, "fallback"
+
+
+def measured_hbm():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, copy)"
+    except Exception:
+        return 6650.0, "fallback"
 
 
 def cpu_baseline(w, target_seconds=12.0):
@@ -192,9 +210,18 @@ def main():
     dev = torch.device("cuda", local_rank)
     dt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype_name]
 
+    decode = Sq == 1
     g = torch.Generator().manual_seed(1234 + rank)
-    host = [torch.randn(B, S, H, D, generator=g).to(dt).pin_memory() for S, H in ((Sq, Hq), (Skv, Hkv), (Skv, Hkv))]
-    Q, K, V = (t.to(dev) for t in host)
+    if decode:
+        # GBs of K/V: generated on the device; the end-to-end leg moves Q and O only (K/V are a resident cache)
+        gd = torch.Generator(device=dev).manual_seed(1234 + rank)
+        Q = torch.randn(B, Sq, Hq, D, generator=gd, device=dev).to(dt)
+        K = torch.randn(B, Skv, Hkv, D, generator=gd, device=dev, dtype=dt)
+        V = torch.randn(B, Skv, Hkv, D, generator=gd, device=dev, dtype=dt)
+        host = [Q.cpu().pin_memory()]
+    else:
+        host = [torch.randn(B, S, H, D, generator=g).to(dt).pin_memory() for S, H in ((Sq, Hq), (Skv, Hkv), (Skv, Hkv))]
+        Q, K, V = (t.to(dev) for t in host)
     host_out = torch.empty(B, Sq, Hq, D, dtype=dt).pin_memory()
 
     if args.impl == "ours":
@@ -223,7 +250,10 @@ def main():
             ao.ref_gpu_fixed(Q, K, V, causal, out=O_pre)
 
     def step_e2e():
-        q, k, v = (t.to(dev, non_blocking=True) for t in host)
+        if decode:
+            q, k, v = host[0].to(dev, non_blocking=True), K, V
+        else:
+            q, k, v = (t.to(dev, non_blocking=True) for t in host)
         if args.impl == "ours":
             o = tf.flash_attn_forward(q, k, v, is_causal=causal)
         else:
@@ -280,7 +310,28 @@ def main():
     bytes_in = (B * Sq * Hq * D + 2 * B * Skv * Hkv * D) * esize
     bytes_out = B * Sq * Hq * D * esize
 
-    if rank == 0:
+    if decode and rank == 0:
+        kv_bytes = 2.0 * B * Skv * Hkv * D * esize
+        hbm, hbm_src = measured_hbm()
+        line = {
+            "metric": "attention fwd decode GB/s (K and V read once)", "value": world * kv_bytes / (ms_step * 1e-3) / 1e9,
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+            "config": {"workload": args.workload, "layout": "[B,S,H,D]", "causal": causal, "batch_per_gpu": B,
+                       "seq_q": Sq, "seq_kv": Skv, "heads_q": Hq, "heads_kv": Hkv, "head_dim": D,
+                       "l2": "K,V = %.2f GB per step > 126 MB L2; no flush" % (kv_bytes / 1e9)},
+            "roofline": {"bound": "hbm", "achieved": kv_bytes / (ms_kernel * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                         "frac": kv_bytes / (ms_kernel * 1e-3) / 1e9 / hbm,
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if args.impl == "ours" else None, "peak_source": hbm_src,
+                         "kernel_ms": ms_kernel},
+            "e2e": {"value": world * kv_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": B * Sq * Hq * D * esize, "d2h_bytes_per_step": bytes_out, "ms_per_step": ms_e2e},
+            "gpu_launches": args.steps, "clocks": clocks,
+        }
+        if args.impl == "reference":
+            line["impl"] = "reference"
+        print(json.dumps(line))
+    elif rank == 0:
         line = {
             "metric": "attention fwd TFLOPS (bf16/fp16 hd128 seq4096)", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -290,7 +341,9 @@ def main():
                        "l2": "Q,K,V,O = 256 MiB per step > 126 MB L2; no flush", "per_gpu_tflops": value / world,
                        "pct_of_nominal_2250": 100.0 * value / world / 2250.0},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if args.impl == "ours" else None,
+                         "peak_source": peak_src,
                          "kernel_ms": ms_kernel},
             "e2e": {"value": world * fl / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in,
                     "d2h_bytes_per_step": bytes_out, "ms_per_step": ms_e2e},
