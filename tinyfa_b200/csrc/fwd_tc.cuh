@@ -21,7 +21,8 @@
 //
 // Tensor memory columns (fp32 words per lane; lane = query row of the tile):
 //   [t*128, t*128+128)            S of Q tile t; the 16-bit P overwrites the first 64 columns
-//   [256 + t*HDP, 256+(t+1)*HDP)  O of Q tile t (NT == 2, HDP <= 128), or [128, 128+HDP) when NT == 1
+//   [256 + t*HDP, 256+(t+1)*HDP)  O of Q tile t (NT == 2, HDP == 128), or [128, 128+HDP) when NT == 1
+//   HDP == 64: 192 columns per tile with S alternating between two positions (see Cfg::kRot), O at 384 + t*64
 #pragma once
 
 #include <cuda.h>
@@ -75,7 +76,13 @@ struct Cfg {
   static constexpr int kNT = (HDP <= 128) ? 2 : 1;       // Q tiles per CTA
   static constexpr int kStages = (HDP == 64) ? 6 : (HDP == 128) ? 4 : (HDP == 192) ? 3 : 2;
   static constexpr int kTmemCols = 512;
-  static constexpr int kOCol0 = (kNT == 2) ? 256 : 128;
+  // HDP == 64 leaves tensor memory to spare, which buys a second S position per tile: S of block j sits at
+  // columns [0,128) (j even) or [64,192) (j odd) of the tile's 192-column region and P of block j in the 64 columns
+  // that the next S does not cover ([0,64) or [128,192)).  Q.K^T of block j+1 can then be issued as soon as the
+  // softmax has read S of block j, instead of after P.V of block j: the softmax never waits for the tensor pipe.
+  static constexpr bool kRot = (HDP == 64);
+  static constexpr int kSRegion = kRot ? 192 : 128;                       // columns per tile for S / P
+  static constexpr int kOCol0 = kRot ? 384 : ((kNT == 2) ? 256 : 128);
   static constexpr int kSmemBytes = (kNT + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
 };
 
@@ -90,7 +97,8 @@ enum Bar : int {
   kBarP1Ready = 12,   // [2]  second half of P written (4 softmax warps)
   kBarKvFull = 14,    // [kStages]
   kBarKvEmpty = 22,   // [kStages]
-  kNumBars = 30,
+  kBarSFree = 30,     // [2]  softmax has read S into registers (rotating-S mode only)
+  kNumBars = 32,
 };
 
 // Optional timeline instrumentation (debug builds only, -DTFA_TRACE): one CTA records clock64() at named points.
@@ -296,6 +304,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::mbar_init(bar(kBarP0Ready + t), 4);
       ptx::mbar_init(bar(kBarP1Ready + t), 4);
       ptx::mbar_init(bar(kBarTurn + t), 1);
+      ptx::mbar_init(bar(kBarSFree + t), 4);
       ptx::mbar_init(bar(kBarPvDone + t), 1);
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
     }
@@ -331,7 +340,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int t = warp >> 2;
     if (t < NT && w.nblk[t] > 0) {
       const int r = threadIdx.x & 127;
-      const uint32_t tS = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(t * 128);
+      const uint32_t tRegion = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(t * C::kSRegion);
       const int qpos = w.qlo[t] + (r >> p.packShift);
       const float c = p.scaleLog2;
       float m = -INFINITY, l = 0.f;
@@ -342,8 +351,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if ((warp & 3) == 0) TFA_TR(t, j, 0);
         uint32_t v[4][32];
 #pragma unroll
+        const uint32_t tS = tRegion + (C::kRot ? (uint32_t)((j & 1) * 64) : 0u);   // S of this block
+        const uint32_t tP = tRegion + (C::kRot ? (uint32_t)((j & 1) * 128) : 0u);  // where its P goes
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
+        if constexpr (C::kRot) {  // S is in registers: the next Q.K^T may overwrite it
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar(kBarSFree + t));
+        }
         if ((warp & 3) == 0) TFA_TR(t, j, 1);
 
         const int kbase = j * kBlockN;
@@ -423,7 +439,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
           }
           if ((warp & 3) == 0) TFA_TR(t, j, 4 + 2 * half);
-          ptx::tmem_st_32x32b_x32(tS + half * 32, pk);
+          ptx::tmem_st_32x32b_x32(tP + half * 32, pk);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
@@ -496,10 +512,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // Issue helpers.  The tensor pipe overlaps at most one MMA with the issuing thread's next instructions, so
       // everything between two tcgen05.mma costs tensor time: per MMA there is one 32-bit add on a descriptor word.
       const uint32_t qLo = kLoT | ((sQ + (uint32_t)(warp != 12) * C::kTileBytes) >> 4);
-      const uint32_t dS = tmem + (uint32_t)((warp != 12) * 128);
+      const uint32_t dRegion = tmem + (uint32_t)((warp != 12) * C::kSRegion);
       const uint32_t dO = tmem + (uint32_t)(C::kOCol0 + (warp != 12) * HDP);
-      auto issueQK = [&](uint32_t kAddr, int part) {  // part 0 / 1: first / second half of the k-steps
+      auto issueQK = [&](int blk, uint32_t kAddr, int part) {  // part 0 / 1: first / second half of the k-steps
         const uint32_t kLo = kLoT | (kAddr >> 4);
+        const uint32_t dS = dRegion + (C::kRot ? (uint32_t)((blk & 1) * 64) : 0u);
 #pragma unroll
         for (int k2 = 0; k2 < HDP / 32; k2++) {
           const int kk = part * (HDP / 32) + k2;
@@ -507,12 +524,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::mma_ss_lohi(dS, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
         }
       };
-      auto issuePV = [&](uint32_t vAddr, uint32_t firstAcc, int half) {  // firstAcc: accumulate flag of k-step 0
+      auto issuePV = [&](int blk, uint32_t vAddr, uint32_t firstAcc, int half) {  // firstAcc: accumulate flag of k-step 0
         const uint32_t vLo = vLoT | (vAddr >> 4);
+        const uint32_t aP = dRegion + (C::kRot ? (uint32_t)((blk & 1) * 128) : 0u);
 #pragma unroll
         for (int k4 = 0; k4 < kBlockN / 32; k4++) {
           const int kk = half * (kBlockN / 32) + k4;
-          ptx::mma_ts_lohi(dO, dS + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, kk == 0 ? firstAcc : 1u);
+          ptx::mma_ts_lohi(dO, aP + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, kk == 0 ? firstAcc : 1u);
         }
       };
 
@@ -537,7 +555,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // tiles drift into lock-step and share both the MUFU and the tensor pipe at the same time.  Turn k of A
       // needs turn k-1 of B, turn k of B needs turn k of A; a thread does its data waits before asking for the
       // token and releases ring stages after passing it on, so those latencies overlap the other thread's issue.
-      const bool dual = (NT == 2) && w.nblk[0] > 0 && w.nblk[1] > 0;
+      const bool dual = (NT == 2) && !C::kRot && w.nblk[0] > 0 && w.nblk[1] > 0;
       const uint32_t myTurn = bar(kBarTurn + t), otherTurn = bar(kBarTurn + (t ^ 1));
       auto takeTurn = [&](int k) {
         if (!dual) return;
@@ -560,8 +578,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         takeTurn(0);
         if (n > 0) {
-          issueQK(sKV + s0 * C::kTileBytes, 0);
-          issueQK(sKV + s0 * C::kTileBytes, 1);
+          issueQK(0, sKV + s0 * C::kTileBytes, 0);
+          issueQK(0, sKV + s0 * C::kTileBytes, 1);
           ptx::tc_commit(bar(kBarSFull + t));
         }
         passTurn();
@@ -576,6 +594,34 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const int sK = ld % NS;
         const uint32_t phK = (ld / NS) & 1;
         bool p1Ready = false;
+        if constexpr (C::kRot) {
+          // rotating S: the next scores first (they only wait for the softmax to have read the current ones),
+          // then P.V of the current block whenever its P arrives
+          if (j + 1 < n) {
+            wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
+            wait_bar(bar(kBarSFree + t), j & 1, wc, 18);
+            ptx::tc_fence_after();
+            issueQK(j + 1, sKV + sK * C::kTileBytes, 0);
+            issueQK(j + 1, sKV + sK * C::kTileBytes, 1);
+            ptx::tc_commit(bar(kBarSFull + t));
+          }
+          if (j < n) {
+            wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
+            wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
+            ptx::tc_fence_after();
+            issuePV(j, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
+            wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
+            ptx::tc_fence_after();
+            issuePV(j, sKV + sV * C::kTileBytes, 1u, 1);
+            ptx::tc_commit(bar(kBarPvDone + t));
+          }
+          release(sV, phV, j < n);
+          if (hasNext) {
+            release(sK, phK, j + 1 < n);
+            ld++;
+          }
+          continue;
+        }
         if (j < n) {
           wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
           if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
@@ -589,18 +635,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (j < n) {
           ptx::tc_fence_after();
           TFA_TR(3, j, t * 4 + 0);
-          issuePV(sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
+          issuePV(j, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
           if (!p1Ready) {
             wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
             ptx::tc_fence_after();
           }
           TFA_TR(3, j, t * 4 + 1);
-          issuePV(sKV + sV * C::kTileBytes, 1u, 1);
+          issuePV(j, sKV + sV * C::kTileBytes, 1u, 1);
           TFA_TR(3, j, t * 4 + 2);
           if (j + 1 < n) {
-            issueQK(sKV + sK * C::kTileBytes, 0);
+            issueQK(j + 1, sKV + sK * C::kTileBytes, 0);
             passTurn();
-            issueQK(sKV + sK * C::kTileBytes, 1);
+            issueQK(j + 1, sKV + sK * C::kTileBytes, 1);
             ptx::tc_commit(bar(kBarSFull + t));
             TFA_TR(3, j, t * 4 + 3);
           } else {
