@@ -319,9 +319,9 @@ int launch_fwd_fp32(const FwdProblem& pr) {
     case 128:
       return fp32::launch<128, 64>(pr);
     case 192:
-      return fp32::launch<192, 32>(pr);
+      return fp32::launch<192, 64>(pr);
     case 256:
-      return fp32::launch<256, 32>(pr);
+      return fp32::launch<256, 64>(pr);
     default:
       return kBadHeadDim;
   }

@@ -149,6 +149,27 @@ __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, const Wa
   }
 }
 
+// Same contract as wait_bar, polling with the non-blocking test_wait: lower wake-up latency, at the price of
+// issue slots - used only by the single-thread MMA issuers, whose reaction time is on the critical path.
+__device__ __forceinline__ void spin_bar(uint32_t bar, uint32_t parity, const WaitCtx& c, int site) {
+  if (ptx::mbar_test_wait(bar, parity)) return;
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!ptx::mbar_test_wait(bar, parity)) {
+    if ((++spins & 0x3FFF) == 0) {
+      if (*c.failed) return;
+      const uint64_t now = ptx::global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2000000000ull) {
+        *c.failed = 1;
+        atomicExch(c.status, (c.epoch << 8) | site);
+        return;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -560,9 +581,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       auto takeTurn = [&](int k) {
         if (!dual) return;
         if (t == 0) {
-          if (k > 0) wait_bar(myTurn, (k - 1) & 1, wc, 16);
+          if (k > 0) spin_bar(myTurn, (k - 1) & 1, wc, 16);
         } else {
-          wait_bar(myTurn, k & 1, wc, 17);
+          spin_bar(myTurn, k & 1, wc, 17);
         }
       };
       auto passTurn = [&]() {
@@ -625,8 +646,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (j < n) {
           wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
           if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
-          wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
-          p1Ready = ptx::mbar_try_wait(bar(kBarP1Ready + t), j & 1);
+          spin_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
+          p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + t), j & 1);
         }
         takeTurn(j + 1);
         // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
@@ -637,7 +658,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           TFA_TR(3, j, t * 4 + 0);
           issuePV(j, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
           if (!p1Ready) {
-            wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
+            spin_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
             ptx::tc_fence_after();
           }
           TFA_TR(3, j, t * 4 + 1);
