@@ -64,6 +64,15 @@ constexpr int kIssuerB = TFA_ISSUER_B;  // warp that issues the MMAs of Q tile 1
 #ifndef TFA_EMU_COUNT
 #define TFA_EMU_COUNT 1
 #endif
+#ifdef TFA_SPIN_SFULL
+#define TFA_SFULL_WAIT spin_bar
+#else
+#define TFA_SFULL_WAIT wait_bar
+#endif
+#ifndef TFA_SPECULATE
+#define TFA_SPECULATE 0
+#endif
+constexpr bool kSpeculate = TFA_SPECULATE != 0;
 constexpr int kEmuPeriod = 8;              // of every kEmuPeriod pairs of exponentials ...
 constexpr int kEmuCount = TFA_EMU_COUNT;   // ... this many are evaluated on the FMA pipe instead of the MUFU
 constexpr float kRescaleLog2 = 8.0f;  // lazy-rescale threshold, log2 units
@@ -367,13 +376,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       float m = -INFINITY, l = 0.f;
       const int n = w.nblk[t];
       for (int j = 0; j < n; j++) {
-        wait_bar(bar(kBarSFull + t), j & 1, wc, 1);
+        TFA_SFULL_WAIT(bar(kBarSFull + t), j & 1, wc, 1);
         ptx::tc_fence_after();
         if ((warp & 3) == 0) TFA_TR(t, j, 0);
         uint32_t v[4][32];
-#pragma unroll
         const uint32_t tS = tRegion + (C::kRot ? (uint32_t)((j & 1) * 64) : 0u);   // S of this block
         const uint32_t tP = tRegion + (C::kRot ? (uint32_t)((j & 1) * 128) : 0u);  // where its P goes
+#pragma unroll
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
         if constexpr (C::kRot) {  // S is in registers: the next Q.K^T may overwrite it
@@ -396,6 +405,33 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
           }
         }
+        // Exponentials of one 32-key quarter: 16 pairs -> 16 packed 16-bit words, plus their (unrounded) sum.
+        const float2 c2 = make_float2(c, c);
+        auto expQuarter = [&](const uint32_t(&vq)[32], float negMc, uint32_t(&dst)[16], float2& sum) {
+          const float2 negMc2 = make_float2(negMc, negMc);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float2 x = make_float2(__uint_as_float(vq[i]), __uint_as_float(vq[i + 1]));
+            x = ffma2(x, c2, negMc2);
+            if (((i >> 1) % kEmuPeriod) < kEmuCount) {  // compile-time pattern: this pair goes to the FMA pipe
+              x = ex2_fma2(x);
+            } else {
+              x.x = ex2(x.x);
+              x.y = ex2(x.y);
+            }
+            sum = fadd2(sum, x);
+            dst[i >> 1] = pack2<kBf16>(x.x, x.y);
+          }
+        };
+        // Speculation: from the second block on, the first quarter's exponentials are started against the OLD
+        // reference max, so that the MUFU works while the row max of this block is still being reduced; the
+        // lazy-rescale rule makes the old max the final one in all but rare cases, which redo the quarter.
+        uint32_t pkA[16], pkB[16];
+        float2 sumQ0 = make_float2(0.f, 0.f);
+        const bool spec = kSpeculate && (j > 0);
+        const float mUseOld = (m == -INFINITY) ? 0.f : m;
+        if (spec) expQuarter(v[0], -mUseOld * c, pkA, sumQ0);
+
         // row max: four independent chains of 3-input max
         float mx4[4];
 #pragma unroll
@@ -436,31 +472,23 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         m = mNew;
         if ((warp & 3) == 0) TFA_TR(t, j, 3);
 
-        const float2 c2 = make_float2(c, c);
-        const float2 negMc2 = make_float2(-mUse * c, -mUse * c);
-        float2 sum2 = make_float2(0.f, 0.f);
+        const float negMc = -mUse * c;
+        if (!spec || mUse != mUseOld) {
+          sumQ0 = make_float2(0.f, 0.f);
+          expQuarter(v[0], negMc, pkA, sumQ0);
+        }
+        float2 sum2 = sumQ0;
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int qq = 0; qq < 2; qq++) {
-            const int q = half * 2 + qq;
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float2 x = make_float2(__uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
-              x = ffma2(x, c2, negMc2);
-              if (((i >> 1) % kEmuPeriod) < kEmuCount) {  // compile-time pattern: this pair goes to the FMA pipe
-                x = ex2_fma2(x);
-              } else {
-                x.x = ex2(x.x);
-                x.y = ex2(x.y);
-              }
-              sum2 = fadd2(sum2, x);
-              pk[qq * 16 + (i >> 1)] = pack2<kBf16>(x.x, x.y);
-            }
+          if (half == 0) {
+            expQuarter(v[1], negMc, pkB, sum2);
+          } else {
+            expQuarter(v[2], negMc, pkA, sum2);
+            expQuarter(v[3], negMc, pkB, sum2);
           }
           if ((warp & 3) == 0) TFA_TR(t, j, 4 + 2 * half);
-          ptx::tmem_st_32x32b_x32(tP + half * 32, pk);
+          ptx::tmem_st_32x32b_x16(tP + half * 32, pkA);
+          ptx::tmem_st_32x32b_x16(tP + half * 32 + 16, pkB);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
