@@ -66,7 +66,10 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
-// One status word per device, allocated on first use and kept for the life of the process.
+// One small block of ints per device, allocated on first use and kept for the life of the process:
+// word 0 is the status word, words 1..kWorkCounters are work counters of the persistent kernel (one per launch
+// in flight, picked by launch epoch and zeroed on the launch stream).
+constexpr int kWorkCounters = 64;
 static std::mutex g_devMutex;
 static int* g_statusWord[64] = {nullptr};
 static int g_devChecked[64] = {0};  // 0 = unknown, 1 = cc 10.x, -1 = other
@@ -76,13 +79,37 @@ int* device_status_word(int device) {
   if (device < 0 || device >= 64) return nullptr;
   if (g_statusWord[device] == nullptr) {
     int* p = nullptr;
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess || cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&p, sizeof(int) * (1 + kWorkCounters)) != cudaSuccess ||
+        cudaMemset(p, 0, sizeof(int) * (1 + kWorkCounters)) != cudaSuccess) {
       set_error_string("could not allocate the device status word: %s", cudaGetErrorString(cudaGetLastError()));
       return nullptr;
     }
     g_statusWord[device] = p;
   }
   return g_statusWord[device];
+}
+
+// Work counter for one launch: zeroed behind everything already enqueued on `stream`.
+int* device_work_counter(int device, int epoch, cudaStream_t stream) {
+  int* base = device_status_word(device);
+  if (base == nullptr) return nullptr;
+  int* counter = base + 1 + (epoch % kWorkCounters);
+  if (cudaMemsetAsync(counter, 0, sizeof(int), stream) != cudaSuccess) {
+    set_error_string("cudaMemsetAsync(work counter): %s", cudaGetErrorString(cudaGetLastError()));
+    return nullptr;
+  }
+  return counter;
+}
+
+int device_num_sms(int device) {
+  static int cached[64] = {0};
+  if (device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    cached[device] = n;
+  }
+  return cached[device];
 }
 
 int check_device() {

@@ -45,7 +45,10 @@ struct TcParams {
   int headDim;    // true head dim (<= HDP)
   int group;      // headsQ / headsKV
   int packShift;  // log2 of the number of Q heads interleaved into one 128-row tile
-  int numPairs;   // gridDim.x
+  int numPairs;   // query tile pairs per sequence (from the maximum length)
+  int numUnits;   // Q head units (headsQ >> packShift)
+  int numWork;    // numPairs * numUnits * batch
+  int* workCounter;  // device counter, zero at launch: next work item
   int causal;
   float scaleLog2;  // log2(e) / sqrt(headDim)
   int* status;      // device status word
@@ -107,7 +110,11 @@ enum Bar : int {
   kBarKvFull = 14,    // [kStages]
   kBarKvEmpty = 22,   // [kStages]
   kBarSFree = 30,     // [2]  softmax has read S into registers (rotating-S mode only)
-  kNumBars = 32,
+  kBarQEmpty = 32,    // [2]  last Q.K^T of the item finished: the Q tile may be overwritten (tcgen05.commit)
+  kBarOFree = 34,     // [2]  epilogue has read O of the item into registers (4 epilogue warps)
+  kBarWorkFull = 36,  // [2]  loader published the next work item in slot k & 1
+  kBarWorkEmpty = 38, // [2]  every consumer has read the slot
+  kNumBars = 40,
 };
 
 // Optional timeline instrumentation (debug builds only, -DTFA_TRACE): one CTA records clock64() at named points.
@@ -124,11 +131,14 @@ __device__ unsigned long long g_trace[kTraceRoles * kTraceIters * kTracePts];
   } while (0)
 #endif
 
+constexpr int kWorkConsumers = 14;  // 8 softmax warps + 4 epilogue warps + 2 MMA-issuing threads
+
 struct Ctl {
   uint64_t bars[kNumBars];
   float scale[2][kBlockM];
   uint32_t tmemBase;
   int failed;
+  int work[2];
 };
 
 struct WaitCtx {
@@ -264,11 +274,15 @@ struct Work {
   int nmax;
 };
 
+// Work item idx -> (query tile pair, Q head unit, batch entry); pair index fastest so that CTAs running at the
+// same time share K/V through L2, heavy (late) causal pairs of a head first.
 template <int NT>
-__device__ __forceinline__ bool make_work(const TcParams& p, Work& w) {
-  const int pairIdx = p.causal ? (p.numPairs - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // heavy tiles first
-  w.unit = blockIdx.y;
-  const int b = blockIdx.z;
+__device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
+  const int pr = idx % p.numPairs;
+  const int rest = idx / p.numPairs;
+  const int pairIdx = p.causal ? (p.numPairs - 1 - pr) : pr;
+  w.unit = rest % p.numUnits;
+  const int b = rest / p.numUnits;
   if (p.cuQ != nullptr) {
     const int q0 = p.cuQ[b], q1 = p.cuQ[b + 1], k0 = p.cuKV[b], k1 = p.cuKV[b + 1];
     w.qRow0 = q0;
@@ -283,10 +297,11 @@ __device__ __forceinline__ bool make_work(const TcParams& p, Work& w) {
   }
   const int rows = kBlockM >> p.packShift;  // sequence positions per tile
   const int seq0 = pairIdx * NT * rows;
+  w.nmax = 0;
+  w.nblk[0] = w.nblk[1] = 0;
   if (seq0 >= w.sq || w.skv <= 0) return false;
   w.hkv = (w.unit << p.packShift) / p.group;
   const int nTotal = (w.skv + kBlockN - 1) / kBlockN;
-  w.nmax = 0;
 #pragma unroll
   for (int t = 0; t < 2; t++) {
     w.qlo[t] = seq0 + t * rows;
@@ -301,6 +316,9 @@ __device__ __forceinline__ bool make_work(const TcParams& p, Work& w) {
   return true;
 }
 
+// Persistent kernel: gridDim.x CTAs (one per SM) pull work items from a global counter until it runs out, so the
+// prologue of the next item (Q/K/V loads, first Q.K^T) overlaps the epilogue of the current one.  Every mbarrier keeps
+// running across items; each role tracks phases with its own running counters.
 template <int HDP, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -309,10 +327,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   constexpr int NT = C::kNT;
   constexpr int NS = C::kStages;
   static_assert(NS <= 8, "barrier slots");
-
-  Work w;
-  if (!make_work<NT>(p, w)) return;  // uniform for the CTA: nothing allocated yet
-  if ((*p.status >> 8) == p.epoch) return;  // an earlier CTA of this launch already gave up: drain quickly
 
   extern __shared__ uint8_t smemRaw[];
   const uint32_t rawAddr = ptx::smem_u32(smemRaw);
@@ -330,6 +344,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int t = 0; t < 2; t++) {
       ptx::mbar_init(bar(kBarQFull + t), 1);
+      ptx::mbar_init(bar(kBarQEmpty + t), 1);
       ptx::mbar_init(bar(kBarSFull + t), 1);
       ptx::mbar_init(bar(kBarP0Ready + t), 4);
       ptx::mbar_init(bar(kBarP1Ready + t), 4);
@@ -337,6 +352,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::mbar_init(bar(kBarSFree + t), 4);
       ptx::mbar_init(bar(kBarPvDone + t), 1);
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
+      ptx::mbar_init(bar(kBarOFree + t), 4);
+      ptx::mbar_init(bar(kBarWorkFull + t), 1);
+      ptx::mbar_init(bar(kBarWorkEmpty + t), kWorkConsumers);
     }
     for (int s = 0; s < NS; s++) {
       ptx::mbar_init(bar(kBarKvFull + s), 1);
@@ -361,27 +379,44 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tmem = ctl->tmemBase;
   const WaitCtx wc{&ctl->failed, p.status, p.epoch};
 #ifdef TFA_TRACE
-  const bool traceOn = (blockIdx.x == gridDim.x / 2) && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+  const bool traceOn = (blockIdx.x == gridDim.x / 2) && lane == 0;
 #endif
+
+  // Every consumer of work items (8 softmax warps, 4 epilogue warps, 2 MMA threads) reads item k from slot k & 1
+  // and frees the slot; a negative index ends the loop.
+  auto fetchWork = [&](int k) -> int {
+    wait_bar(bar(kBarWorkFull + (k & 1)), (k >> 1) & 1, wc, 20);
+    const int idx = *reinterpret_cast<volatile int*>(&ctl->work[k & 1]);
+    return idx;
+  };
 
   if (warp < 8) {
     // ================================================================ softmax
     ptx::setmaxnreg_inc<176>();
     const int t = warp >> 2;
-    if (t < NT && w.nblk[t] > 0) {
-      const int r = threadIdx.x & 127;
-      const uint32_t tRegion = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(t * C::kSRegion);
+    const int r = threadIdx.x & 127;
+    const uint32_t tRegion = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(t * C::kSRegion);
+    const float c = p.scaleLog2;
+    int it = 0;      // blocks of this tile processed so far, over all work items (phase of the per-block barriers)
+    int items = 0;   // work items in which this tile was active
+    for (int k = 0;; k++) {
+      const int idx = fetchWork(k);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
+      if (idx < 0 || *wc.failed) break;
+      Work w;
+      if (!make_work<NT>(p, idx, w)) continue;
+      if (t >= NT || w.nblk[t] == 0) continue;
       const int qpos = w.qlo[t] + (r >> p.packShift);
-      const float c = p.scaleLog2;
       float m = -INFINITY, l = 0.f;
       const int n = w.nblk[t];
-      for (int j = 0; j < n; j++) {
-        TFA_SFULL_WAIT(bar(kBarSFull + t), j & 1, wc, 1);
+      for (int j = 0; j < n; j++, it++) {
+        wait_bar(bar(kBarSFull + t), it & 1, wc, 1);
         ptx::tc_fence_after();
-        if ((warp & 3) == 0) TFA_TR(t, j, 0);
+        if ((warp & 3) == 0) TFA_TR(t, it, 0);
         uint32_t v[4][32];
-        const uint32_t tS = tRegion + (C::kRot ? (uint32_t)((j & 1) * 64) : 0u);   // S of this block
-        const uint32_t tP = tRegion + (C::kRot ? (uint32_t)((j & 1) * 128) : 0u);  // where its P goes
+        const uint32_t tS = tRegion + (C::kRot ? (uint32_t)((it & 1) * 64) : 0u);   // S of this block
+        const uint32_t tP = tRegion + (C::kRot ? (uint32_t)((it & 1) * 128) : 0u);  // where its P goes
 #pragma unroll
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
@@ -390,7 +425,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar(kBarSFree + t));
         }
-        if ((warp & 3) == 0) TFA_TR(t, j, 1);
+        if ((warp & 3) == 0) TFA_TR(t, it, 1);
 
         const int kbase = j * kBlockN;
         const bool needMask = (kbase + kBlockN > w.skv) || (p.causal && (kbase + kBlockN - 1 > w.qlo[t]));
@@ -423,9 +458,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             dst[i >> 1] = pack2<kBf16>(x.x, x.y);
           }
         };
-        // Speculation: from the second block on, the first quarter's exponentials are started against the OLD
-        // reference max, so that the MUFU works while the row max of this block is still being reduced; the
-        // lazy-rescale rule makes the old max the final one in all but rare cases, which redo the quarter.
+        // Optional speculation (off by default: measured slower): from the second block on, the first quarter's
+        // exponentials start against the OLD reference max while the row max of this block is still being reduced.
         uint32_t pkA[16], pkB[16];
         float2 sumQ0 = make_float2(0.f, 0.f);
         const bool spec = kSpeculate && (j > 0);
@@ -441,7 +475,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        if ((warp & 3) == 0) TFA_TR(t, j, 2);
+        if ((warp & 3) == 0) TFA_TR(t, it, 2);
         // Lazy rescale: keep the old reference max while the new one exceeds it by less than kRescaleLog2 in
         // the exp2 domain (P then grows up to 2^kRescaleLog2, harmless in fp32 sums and 16-bit P); the
         // result is unchanged because O and the row sum stay relative to the same reference value.
@@ -450,9 +484,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (__any_sync(0xffffffffu, grow)) {
           // Rare: some row of this warp moves its reference max.  Rescale that row's O in tensor memory (rows
           // that keep their max multiply by 1) once the previous P.V has landed; P.V of this block waits for
-          // the P0 arrival below, so it sees the rescaled accumulator.
+          // the P0 arrival below, so it sees the rescaled accumulator.  (A parity wait is only meaningful for the
+          // phase in progress or the one just completed: P.V of block it-2 finished before S of this block was
+          // produced, and P.V of this block cannot start before this warp arrives.)
           const float scale = grow ? ex2((m - mNew) * c) : 1.f;
-          wait_bar(bar(kBarPvDone + t), (j - 1) & 1, wc, 5);
+          wait_bar(bar(kBarPvDone + t), (it - 1) & 1, wc, 5);
           ptx::tc_fence_after();
           const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll 1
@@ -470,7 +506,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (m != -INFINITY && !grow) mNew = m;
         const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
         m = mNew;
-        if ((warp & 3) == 0) TFA_TR(t, j, 3);
+        if ((warp & 3) == 0) TFA_TR(t, it, 3);
 
         const float negMc = -mUse * c;
         if (!spec || mUse != mUseOld) {
@@ -486,62 +522,80 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             expQuarter(v[2], negMc, pkA, sum2);
             expQuarter(v[3], negMc, pkB, sum2);
           }
-          if ((warp & 3) == 0) TFA_TR(t, j, 4 + 2 * half);
+          if ((warp & 3) == 0) TFA_TR(t, it, 4 + 2 * half);
           ptx::tmem_st_32x32b_x16(tP + half * 32, pkA);
           ptx::tmem_st_32x32b_x16(tP + half * 32 + 16, pkB);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + t));
-          if ((warp & 3) == 0) TFA_TR(t, j, 5 + 2 * half);
-          if (t == 0 && (warp & 3) != 0 && half == 0) TFA_TR(2, j, 2 + (warp & 3));
-          if (t == 0 && (warp & 3) != 0 && (warp & 3) < 3 && half == 1) TFA_TR(2, j, 5 + (warp & 3));
+          if ((warp & 3) == 0) TFA_TR(t, it, 5 + 2 * half);
         }
         l += sum2.x + sum2.y;
       }
-      // final row sum for the epilogue
+      // final row sums for the epilogue; the slot is free once the epilogue of the previous item has released O
+      if (items > 0) wait_bar(bar(kBarOFree + t), (items - 1) & 1, wc, 3);
       ctl->scale[t][r] = l;
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
+      items++;
     }
   } else if (warp < 12) {
     // ================================================================ epilogue
     ptx::setmaxnreg_dec<96>();
     const int r = threadIdx.x & 127;
     const uint32_t laneOff = (uint32_t)((warp & 3) * 32) << 16;
-    // epilogue: O / rowsum -> 16-bit -> global
     const int gp = 1 << p.packShift;
+    int items[2] = {0, 0};    // work items in which tile t was active
+    int pvTotal[2] = {0, 0};  // blocks of tile t issued so far
+    for (int k = 0;; k++) {
+      const int idx = fetchWork(k);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
+      if (idx < 0 || *wc.failed) break;
+      Work w;
+      if (!make_work<NT>(p, idx, w)) continue;
 #pragma unroll
-    for (int t = 0; t < NT; t++) {
-      const int n = w.nblk[t];
-      if (n == 0) continue;
-      wait_bar(bar(kBarScaleFull + t), 0, wc, 6);
-      const float l = ctl->scale[t][r];
-      wait_bar(bar(kBarPvDone + t), (n - 1) & 1, wc, 7);
-      ptx::tc_fence_after();
-      const float inv = (l > 0.f) ? (1.f / l) : 0.f;
-      const int qpos = w.qlo[t] + (r >> p.packShift);
-      const int head = (w.unit << p.packShift) + (r & (gp - 1));
-      const bool valid = qpos < w.sq;
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.O) +
-                                            ((w.qRow0 + qpos) * p.headsQ + head) * (long long)p.headDim);
-      const uint32_t tO = tmem + laneOff + (uint32_t)(C::kOCol0 + t * HDP);
+      for (int t = 0; t < NT; t++) {
+        const int n = w.nblk[t];
+        if (n == 0) continue;
+        pvTotal[t] += n;
+        wait_bar(bar(kBarScaleFull + t), items[t] & 1, wc, 6);
+        const float l = ctl->scale[t][r];
+        // Last P.V of the item.  Valid as a parity wait: the softmax published its row sums after storing the
+        // last P, i.e. after all earlier P.V of the tile, and the next item's P.V waits for kBarOFree below.
+        wait_bar(bar(kBarPvDone + t), (pvTotal[t] - 1) & 1, wc, 7);
+        ptx::tc_fence_after();
+        const float inv = (l > 0.f) ? (1.f / l) : 0.f;
+        const int qpos = w.qlo[t] + (r >> p.packShift);
+        const int head = (w.unit << p.packShift) + (r & (gp - 1));
+        const bool valid = qpos < w.sq;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.O) +
+                                              ((w.qRow0 + qpos) * p.headsQ + head) * (long long)p.headDim);
+        const uint32_t tO = tmem + laneOff + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll
-      for (int ch = 0; ch < HDP / 32; ch++) {
-        uint32_t o[32];
-        ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
-        ptx::tmem_wait_ld();
-        if (valid && ch * 32 < p.headDim) {
+        for (int ch = 0; ch < HDP / 32; ch++) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
+          ptx::tmem_wait_ld();
+          if (ch == HDP / 32 - 1) {  // O is in registers: the next item's first P.V may overwrite the accumulator
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kBarOFree + t));
+          }
+          if (valid && ch * 32 < p.headDim) {
 #pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint4 q;
-            q.x = pack2<kBf16>(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
-            q.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
-            q.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
-            q.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
-            dst[ch * 4 + g] = q;
+            for (int g = 0; g < 4; g++) {
+              uint4 q;
+              q.x = pack2<kBf16>(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+              q.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+              q.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+              q.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+              dst[ch * 4 + g] = q;
+            }
           }
         }
+        items[t]++;
       }
     }
   } else {
@@ -555,14 +609,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const uint64_t descK = ptx::smem_desc_sw128(16, 1024);
       // MN-major operand (V, head dim contiguous): 64-wide slabs kTileBytes/kSub apart, 8-key groups 1024 bytes apart.
       const uint64_t descV = ptx::smem_desc_sw128(kSubTileBytes, 1024);
-
       const uint32_t kHi = (uint32_t)(descK >> 32), vHi = (uint32_t)(descV >> 32);
       const uint32_t kLoT = (uint32_t)descK, vLoT = (uint32_t)descV;  // LBO field; start address added below
       // Issue helpers.  The tensor pipe overlaps at most one MMA with the issuing thread's next instructions, so
       // everything between two tcgen05.mma costs tensor time: per MMA there is one 32-bit add on a descriptor word.
-      const uint32_t qLo = kLoT | ((sQ + (uint32_t)(warp != 12) * C::kTileBytes) >> 4);
-      const uint32_t dRegion = tmem + (uint32_t)((warp != 12) * C::kSRegion);
-      const uint32_t dO = tmem + (uint32_t)(C::kOCol0 + (warp != 12) * HDP);
+      const int t = (warp != 12) ? 1 : 0;
+      const uint32_t qLo = kLoT | ((sQ + (uint32_t)t * C::kTileBytes) >> 4);
+      const uint32_t dRegion = tmem + (uint32_t)(t * C::kSRegion);
+      const uint32_t dO = tmem + (uint32_t)(C::kOCol0 + t * HDP);
       auto issueQK = [&](int blk, uint32_t kAddr, int part) {  // part 0 / 1: first / second half of the k-steps
         const uint32_t kLo = kLoT | (kAddr >> 4);
         const uint32_t dS = dRegion + (C::kRot ? (uint32_t)((blk & 1) * 64) : 0u);
@@ -583,12 +637,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       };
 
-      // One issuing thread per Q tile (warp 12: tile 0, warp 14: tile 1).  Every wait and commit costs the issuing
-      // thread ~100 clocks during which it feeds nothing to the tensor pipe; with two issuers the other tile's MMAs
-      // fill those gaps.  Both threads walk the same K0 V0 K1 V1 ... ring; a stage is released by one arrival per
-      // issuer (a tcgen05.commit when the tile used the block, a plain arrive when it did not).
-      const int t = (warp != 12) ? 1 : 0;
-      const int n = (t < NT) ? w.nblk[t] : 0;
+      // One issuing thread per Q tile (warp 12: tile 0, warp kIssuerB: tile 1).  Every wait and commit costs the
+      // issuing thread ~100 clocks during which it feeds nothing to the tensor pipe; with two issuers the other
+      // tile's MMAs fill those gaps.  Both threads walk the same K0 V0 K1 V1 ... ring; a stage is released by one
+      // arrival per issuer (a tcgen05.commit when the tile used the block, a plain arrive when it did not).
       // A thread that does not use a block still waits for it to land before releasing it: that keeps its
       // arrivals in step with the loader, so two arrivals of one thread can never complete a phase on their own.
       auto release = [&](int stage, uint32_t phase, bool used) {
@@ -601,140 +653,185 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       };
       // The two issuers take strict turns (A: tile 0, B: tile 1, A, B, ...), which keeps the two tiles in
       // anti-phase: one tile's softmax runs while the other tile's MMAs run.  Without the turn token the two
-      // tiles drift into lock-step and share both the MUFU and the tensor pipe at the same time.  Turn k of A
-      // needs turn k-1 of B, turn k of B needs turn k of A; a thread does its data waits before asking for the
+      // tiles drift into lock-step and share both the MUFU and the tensor pipe at the same time.  Turn g of A
+      // needs turn g-1 of B, turn g of B needs turn g of A; a thread does its data waits before asking for the
       // token and releases ring stages after passing it on, so those latencies overlap the other thread's issue.
-      const bool dual = (NT == 2) && !C::kRot && w.nblk[0] > 0 && w.nblk[1] > 0;
       const uint32_t myTurn = bar(kBarTurn + t), otherTurn = bar(kBarTurn + (t ^ 1));
-      auto takeTurn = [&](int k) {
-        if (!dual) return;
-        if (t == 0) {
-          if (k > 0) spin_bar(myTurn, (k - 1) & 1, wc, 16);
-        } else {
-          spin_bar(myTurn, k & 1, wc, 17);
-        }
-      };
-      auto passTurn = [&]() {
-        if (dual) ptx::mbar_arrive(otherTurn);
-      };
-      int ld = 0;  // index of the next KV-ring load to consume
-      {
-        const int s0 = ld % NS;
-        if (n > 0) {
-          wait_bar(bar(kBarKvFull + s0), (ld / NS) & 1, wc, 8);
-          wait_bar(bar(kBarQFull + t), 0, wc, 9);
-          ptx::tc_fence_after();
-        }
-        takeTurn(0);
-        if (n > 0) {
-          issueQK(0, sKV + s0 * C::kTileBytes, 0);
-          issueQK(0, sKV + s0 * C::kTileBytes, 1);
-          ptx::tc_commit(bar(kBarSFull + t));
-        }
-        passTurn();
-        release(s0, 0, n > 0);
-        ld++;
-      }
-      for (int j = 0; j < w.nmax; j++) {
-        const int sV = ld % NS;
-        const uint32_t phV = (ld / NS) & 1;
-        ld++;
-        const bool hasNext = (j + 1 < w.nmax);
-        const int sK = ld % NS;
-        const uint32_t phK = (ld / NS) & 1;
-        bool p1Ready = false;
-        if constexpr (C::kRot) {
-          // rotating S: the next scores first (they only wait for the softmax to have read the current ones),
-          // then P.V of the current block whenever its P arrives
-          if (j + 1 < n) {
-            wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
-            wait_bar(bar(kBarSFree + t), j & 1, wc, 18);
-            ptx::tc_fence_after();
-            issueQK(j + 1, sKV + sK * C::kTileBytes, 0);
-            issueQK(j + 1, sKV + sK * C::kTileBytes, 1);
-            ptx::tc_commit(bar(kBarSFull + t));
+      int turn = 0;  // turns taken so far by this thread (same count on both threads)
+      int ld = 0;    // KV-ring loads consumed so far (K0 V0 K1 V1 ... of every item)
+      int it = 0;    // blocks of this tile issued so far
+      int qc = 0;    // work items in which this tile was active
+      for (int k = 0;; k++) {
+        const int idx = fetchWork(k);
+        ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
+        if (idx < 0 || *wc.failed) break;
+        Work w;
+        if (!make_work<NT>(p, idx, w)) continue;
+        const int n = (t < NT) ? w.nblk[t] : 0;
+        const bool dual = (NT == 2) && !C::kRot && w.nblk[0] > 0 && w.nblk[1] > 0;
+        auto takeTurn = [&]() {
+          if (!dual) return;
+          if (t == 0) {
+            if (turn > 0) spin_bar(myTurn, (turn - 1) & 1, wc, 16);
+          } else {
+            spin_bar(myTurn, turn & 1, wc, 17);
           }
+        };
+        auto passTurn = [&]() {
+          if (dual) {
+            ptx::mbar_arrive(otherTurn);
+            turn++;
+          }
+        };
+        {
+          const int s0 = ld % NS;
+          const uint32_t ph0 = (ld / NS) & 1;
+          if (n > 0) {
+            wait_bar(bar(kBarKvFull + s0), ph0, wc, 8);
+            wait_bar(bar(kBarQFull + t), qc & 1, wc, 9);
+            ptx::tc_fence_after();
+          }
+          takeTurn();
+          if (n > 0) {
+            issueQK(it, sKV + s0 * C::kTileBytes, 0);
+            issueQK(it, sKV + s0 * C::kTileBytes, 1);
+            ptx::tc_commit(bar(kBarSFull + t));
+            if (n == 1) ptx::tc_commit(bar(kBarQEmpty + t));  // Q tile no longer needed
+          }
+          passTurn();
+          release(s0, ph0, n > 0);
+          ld++;
+        }
+        for (int j = 0; j < w.nmax; j++) {
+          const int sV = ld % NS;
+          const uint32_t phV = (ld / NS) & 1;
+          ld++;
+          const bool hasNext = (j + 1 < w.nmax);
+          const int sK = ld % NS;
+          const uint32_t phK = (ld / NS) & 1;
+          const int blk = it + j;  // running index of block j of this tile
+          if constexpr (C::kRot) {
+            // rotating S: the next scores first (they only wait for the softmax to have read the current ones),
+            // then P.V of the current block whenever its P arrives
+            if (j + 1 < n) {
+              wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
+              wait_bar(bar(kBarSFree + t), blk & 1, wc, 18);
+              ptx::tc_fence_after();
+              issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
+              issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
+              ptx::tc_commit(bar(kBarSFull + t));
+              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + t));
+            }
+            if (j < n) {
+              wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
+              if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
+              wait_bar(bar(kBarP0Ready + t), blk & 1, wc, 11);
+              ptx::tc_fence_after();
+              issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
+              wait_bar(bar(kBarP1Ready + t), blk & 1, wc, 15);
+              ptx::tc_fence_after();
+              issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
+              ptx::tc_commit(bar(kBarPvDone + t));
+            }
+            release(sV, phV, j < n);
+            if (hasNext) {
+              release(sK, phK, j + 1 < n);
+              ld++;
+            }
+            continue;
+          }
+          bool p1Ready = false;
           if (j < n) {
             wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
-            wait_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
+            if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
+            if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
+            spin_bar(bar(kBarP0Ready + t), blk & 1, wc, 11);
+            p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + t), blk & 1);
+          }
+          takeTurn();
+          // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
+          // ~150 clocks to see it, and its first MMAs then queue behind the rest of this turn instead of finding
+          // the tensor pipe idle.  MMAs of the two tiles touch disjoint tensor memory, so interleaving is harmless.
+          if (j < n) {
             ptx::tc_fence_after();
-            issuePV(j, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
-            wait_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
-            ptx::tc_fence_after();
-            issuePV(j, sKV + sV * C::kTileBytes, 1u, 1);
+            TFA_TR(3, blk, t * 4 + 0);
+            issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
+            if (!p1Ready) {
+              spin_bar(bar(kBarP1Ready + t), blk & 1, wc, 15);
+              ptx::tc_fence_after();
+            }
+            TFA_TR(3, blk, t * 4 + 1);
+            issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
+            TFA_TR(3, blk, t * 4 + 2);
+            if (j + 1 < n) {
+              issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
+              passTurn();
+              issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
+              ptx::tc_commit(bar(kBarSFull + t));
+              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + t));
+              TFA_TR(3, blk, t * 4 + 3);
+            } else {
+              passTurn();
+            }
             ptx::tc_commit(bar(kBarPvDone + t));
+          } else {
+            passTurn();
           }
           release(sV, phV, j < n);
           if (hasNext) {
             release(sK, phK, j + 1 < n);
             ld++;
           }
-          continue;
         }
-        if (j < n) {
-          wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
-          if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
-          spin_bar(bar(kBarP0Ready + t), j & 1, wc, 11);
-          p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + t), j & 1);
-        }
-        takeTurn(j + 1);
-        // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
-        // ~150 clocks to see it, and its first MMAs then queue behind the rest of this turn instead of finding
-        // the tensor pipe idle.  MMAs of the two tiles touch disjoint tensor memory, so interleaving is harmless.
-        if (j < n) {
-          ptx::tc_fence_after();
-          TFA_TR(3, j, t * 4 + 0);
-          issuePV(j, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
-          if (!p1Ready) {
-            spin_bar(bar(kBarP1Ready + t), j & 1, wc, 15);
-            ptx::tc_fence_after();
-          }
-          TFA_TR(3, j, t * 4 + 1);
-          issuePV(j, sKV + sV * C::kTileBytes, 1u, 1);
-          TFA_TR(3, j, t * 4 + 2);
-          if (j + 1 < n) {
-            issueQK(j + 1, sKV + sK * C::kTileBytes, 0);
-            passTurn();
-            issueQK(j + 1, sKV + sK * C::kTileBytes, 1);
-            ptx::tc_commit(bar(kBarSFull + t));
-            TFA_TR(3, j, t * 4 + 3);
-          } else {
-            passTurn();
-          }
-          ptx::tc_commit(bar(kBarPvDone + t));
-        } else {
-          passTurn();
-        }
-        release(sV, phV, j < n);
-        if (hasNext) {
-          release(sK, phK, j + 1 < n);
-          ld++;
-        }
+        it += n;
+        if (n > 0) qc++;
       }
     } else if (warp == 13 && lane == 0) {
-      // ============================================================== TMA loads
+      // ============================================================== work distribution + TMA loads
       const int gp = 1 << p.packShift;
+      int ld = 0;            // KV-ring loads issued so far
+      int qc[2] = {0, 0};    // Q loads issued so far per tile
+      for (int k = 0;; k++) {
+        if (k >= 2) wait_bar(bar(kBarWorkEmpty + (k & 1)), ((k >> 1) - 1) & 1, wc, 21);
+        int idx = atomicAdd(p.workCounter, 1);
+        if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
+        *reinterpret_cast<volatile int*>(&ctl->work[k & 1]) = idx;
+        ptx::mbar_arrive(bar(kBarWorkFull + (k & 1)));
+        if (idx < 0) break;
+        Work w;
+        if (!make_work<NT>(p, idx, w)) continue;
+        // The Q tiles of this item cannot land in shared memory before the previous item's last Q.K^T has
+        // finished; pulling them into L2 now shortens that exposed load at the item boundary.
 #pragma unroll
-      for (int t = 0; t < NT; t++) {
-        if (w.nblk[t] == 0) continue;
-        ptx::mbar_arrive_expect_tx(bar(kBarQFull + t), C::kTileBytes);
+        for (int t = 0; t < NT; t++) {
+          if (w.nblk[t] == 0 || qc[t] == 0) continue;
 #pragma unroll
-        for (int a = 0; a < C::kSub; a++) {
-          ptx::tma_load_3d(sQ + t * C::kTileBytes + a * kSubTileBytes, &tmQ, bar(kBarQFull + t), a * 64,
-                           w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
+          for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_3d(&tmQ, a * 64, w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
         }
-      }
-      const int numLoads = 2 * w.nmax;  // K0 V0 K1 V1 ...
-      for (int i = 0; i < numLoads; i++) {
-        const int s = i % NS;
-        if (i >= NS) wait_bar(bar(kBarKvEmpty + s), ((i / NS) - 1) & 1, wc, 14);
-        TFA_TR(4, i >> 1, (i & 1) * 2);
-        ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
-        const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
-        const int row = (int)(w.kvRow0 + (long long)(i >> 1) * kBlockN);
 #pragma unroll
-        for (int a = 0; a < C::kSub; a++) {
-          ptx::tma_load_3d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row);
+        for (int t = 0; t < NT; t++) {
+          if (w.nblk[t] == 0) continue;
+          if (qc[t] > 0) wait_bar(bar(kBarQEmpty + t), (qc[t] - 1) & 1, wc, 22);
+          ptx::mbar_arrive_expect_tx(bar(kBarQFull + t), C::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < C::kSub; a++) {
+            ptx::tma_load_3d(sQ + t * C::kTileBytes + a * kSubTileBytes, &tmQ, bar(kBarQFull + t), a * 64,
+                             w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
+          }
+          qc[t]++;
+        }
+        const int numLoads = 2 * w.nmax;  // K0 V0 K1 V1 ...
+        for (int i = 0; i < numLoads; i++, ld++) {
+          const int s = ld % NS;
+          if (ld >= NS) wait_bar(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, wc, 14);
+          TFA_TR(4, i >> 1, (i & 1) * 2);
+          ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
+          const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
+          const int row = (int)(w.kvRow0 + (long long)(i >> 1) * kBlockN);
+#pragma unroll
+          for (int a = 0; a < C::kSub; a++) {
+            ptx::tma_load_3d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row);
+          }
         }
       }
     }
@@ -743,6 +840,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 12) {
+    if (*wc.failed) __nanosleep(200000);  // a wait gave up: let whatever is still in flight drain before freeing
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, C::kTmemCols);
   }

@@ -27,6 +27,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn get_encode_tiled();  // c_abi.cu
 int* device_status_word(int device);  // c_abi.cu: per-device status word (device memory)
 int next_epoch();                     // c_abi.cu
+int* device_work_counter(int device, int epoch, cudaStream_t stream);  // c_abi.cu
+int device_num_sms(int device);       // c_abi.cu
 
 #define TFA_CAT3(a, b, c) a##b##c
 #define TFA_NAME(hdp, bf) TFA_CAT3(launch_fwd_tc_hdp##hdp, _bf, bf)
@@ -95,9 +97,19 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   p.status = device_status_word(device);
   p.epoch = next_epoch();
   if (p.status == nullptr) return kCudaError;
+  p.numUnits = pr.headsQ / gp;
+  const long long numWork = (long long)p.numPairs * p.numUnits * pr.batch;
+  if (numWork > 0x7FFFFFFFll) {
+    set_error_string("too many work items (%lld)", numWork);
+    return kTooLarge;
+  }
+  p.numWork = (int)numWork;
+  p.workCounter = device_work_counter(device, p.epoch, pr.stream);
+  if (p.workCounter == nullptr) return kCudaError;
 
-  dim3 grid((unsigned)p.numPairs, (unsigned)(pr.headsQ / gp), (unsigned)pr.batch);
-  kernel<<<grid, tc::kThreads, C::kSmemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
+  // persistent: one CTA per SM (512 tensor-memory columns and ~200 KB of shared memory each)
+  const int ctas = (int)(numWork < device_num_sms(device) ? numWork : device_num_sms(device));
+  kernel<<<dim3((unsigned)ctas), tc::kThreads, C::kSmemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error_string("kernel launch failed: %s", cudaGetErrorString(e));

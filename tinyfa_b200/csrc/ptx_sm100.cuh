@@ -91,6 +91,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smemDst, const void* desc, 
       : "memory");
 }
 
+// Same box pulled into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_3d(const void* desc, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(desc), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- register reallocation
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
