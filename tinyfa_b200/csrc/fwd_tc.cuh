@@ -86,7 +86,13 @@ struct Cfg {
   static constexpr int kSub = HDP / 64;                  // 64-element slabs per row
   static constexpr int kTileBytes = kSub * kSubTileBytes;  // one 128-row tile of Q, K or V
   static constexpr int kNT = (HDP <= 128) ? 2 : 1;       // Q tiles per CTA
-  static constexpr int kStages = (HDP == 64) ? 6 : (HDP == 128) ? 4 : (HDP == 192) ? 3 : 2;
+#ifndef TFA_QBUFS128
+#define TFA_QBUFS128 1
+#endif
+  // Q buffers per tile: with two, the Q tiles of the next work item load while the current item still computes.
+  // HDP == 128 would have to give up a K/V ring stage for that (227 KB of shared memory): measured 12 % slower.
+  static constexpr int kQBufs = (HDP == 64) ? 2 : (HDP == 128) ? TFA_QBUFS128 : 1;
+  static constexpr int kStages = (HDP == 64) ? 6 : (HDP == 128) ? (kQBufs == 2 ? 3 : 4) : (HDP == 192) ? 3 : 2;
   static constexpr int kTmemCols = 512;
   // HDP == 64 leaves tensor memory to spare, which buys a second S position per tile: S of block j sits at
   // columns [0,128) (j even) or [64,192) (j odd) of the tile's 192-column region and P of block j in the 64 columns
@@ -95,26 +101,29 @@ struct Cfg {
   static constexpr bool kRot = (HDP == 64);
   static constexpr int kSRegion = kRot ? 192 : 128;                       // columns per tile for S / P
   static constexpr int kOCol0 = kRot ? 384 : ((kNT == 2) ? 256 : 128);
-  static constexpr int kSmemBytes = (kNT + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
+  static constexpr int kSmemBytes = (kNT * kQBufs + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
 };
 
 // Barrier slots (8 bytes each) inside the control block that follows the tiles.
+// A parity wait can only tell "the phase in progress" from "the phase just completed": a waiter must never fall
+// two phases behind its barrier.  Where a producer may legitimately run two uses ahead (Q tiles with two buffers,
+// P in rotating-S mode) each buffer / position has its own barrier, whose next completion depends on the waiter.
 enum Bar : int {
-  kBarQFull = 0,      // [2]  Q tile landed
-  kBarSFull = 2,      // [2]  S = Q.K^T finished (tcgen05.commit)
-  kBarP0Ready = 4,    // [2]  first half of P written (4 softmax warps; O already rescaled if it had to be)
-  kBarPvDone = 6,     // [2]  O += P.V finished (tcgen05.commit)
-  kBarScaleFull = 8,  // [2]  softmax published the final row sums (once per tile)
-  kBarTurn = 10,      // [2]  issue-turn token of the MMA thread of tile t
-  kBarP1Ready = 12,   // [2]  second half of P written (4 softmax warps)
-  kBarKvFull = 14,    // [kStages]
-  kBarKvEmpty = 22,   // [kStages]
-  kBarSFree = 30,     // [2]  softmax has read S into registers (rotating-S mode only)
-  kBarQEmpty = 32,    // [2]  last Q.K^T of the item finished: the Q tile may be overwritten (tcgen05.commit)
-  kBarOFree = 34,     // [2]  epilogue has read O of the item into registers (4 epilogue warps)
-  kBarWorkFull = 36,  // [2]  loader published the next work item in slot k & 1
-  kBarWorkEmpty = 38, // [2]  every consumer has read the slot
-  kNumBars = 40,
+  kBarQFull = 0,       // [tile][Q buffer]  Q tile landed
+  kBarQEmpty = 4,      // [tile][Q buffer]  last Q.K^T of the item finished: buffer may be overwritten (tcgen05.commit)
+  kBarP0Ready = 8,     // [tile][S position] first half of P written (4 softmax warps; O already rescaled if needed)
+  kBarP1Ready = 12,    // [tile][S position] second half of P written (4 softmax warps)
+  kBarSFull = 16,      // [2]  S = Q.K^T finished (tcgen05.commit)
+  kBarPvDone = 18,     // [2]  O += P.V finished (tcgen05.commit)
+  kBarScaleFull = 20,  // [2]  softmax published the final row sums (once per tile and item)
+  kBarTurn = 22,       // [2]  issue-turn token of the MMA thread of tile t
+  kBarSFree = 24,      // [2]  softmax has read S into registers (rotating-S mode only)
+  kBarOFree = 26,      // [2]  epilogue has read O of the item into registers (4 epilogue warps)
+  kBarWorkFull = 28,   // [2]  loader published the next work item in slot k & 1
+  kBarWorkEmpty = 30,  // [2]  every consumer has read the slot
+  kBarKvFull = 32,     // [kStages]
+  kBarKvEmpty = 40,    // [kStages]
+  kNumBars = 48,
 };
 
 // Optional timeline instrumentation (debug builds only, -DTFA_TRACE): one CTA records clock64() at named points.
@@ -333,8 +342,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tileAddr = (rawAddr + 1023u) & ~1023u;  // swizzle-128B slabs need 1024-byte alignment
   uint8_t* smem = smemRaw + (tileAddr - rawAddr);
   const uint32_t sQ = tileAddr;
-  const uint32_t sKV = tileAddr + NT * C::kTileBytes;
-  Ctl* ctl = reinterpret_cast<Ctl*>(smem + (NT + NS) * C::kTileBytes);
+  const uint32_t sKV = tileAddr + NT * C::kQBufs * C::kTileBytes;
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + (NT * C::kQBufs + NS) * C::kTileBytes);
   const uint32_t barBase = ptx::smem_u32(&ctl->bars[0]);
   auto bar = [&](int slot) { return barBase + 8u * (uint32_t)slot; };
 
@@ -343,11 +352,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (threadIdx.x == 0) {
     for (int t = 0; t < 2; t++) {
-      ptx::mbar_init(bar(kBarQFull + t), 1);
-      ptx::mbar_init(bar(kBarQEmpty + t), 1);
+      for (int u = 0; u < 2; u++) {
+        ptx::mbar_init(bar(kBarQFull + 2 * t + u), 1);
+        ptx::mbar_init(bar(kBarQEmpty + 2 * t + u), 1);
+        ptx::mbar_init(bar(kBarP0Ready + 2 * t + u), 4);
+        ptx::mbar_init(bar(kBarP1Ready + 2 * t + u), 4);
+      }
       ptx::mbar_init(bar(kBarSFull + t), 1);
-      ptx::mbar_init(bar(kBarP0Ready + t), 4);
-      ptx::mbar_init(bar(kBarP1Ready + t), 4);
       ptx::mbar_init(bar(kBarTurn + t), 1);
       ptx::mbar_init(bar(kBarSFree + t), 4);
       ptx::mbar_init(bar(kBarPvDone + t), 1);
@@ -417,6 +428,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         uint32_t v[4][32];
         const uint32_t tS = tRegion + (C::kRot ? (uint32_t)((it & 1) * 64) : 0u);   // S of this block
         const uint32_t tP = tRegion + (C::kRot ? (uint32_t)((it & 1) * 128) : 0u);  // where its P goes
+        const int pSlot = C::kRot ? (it & 1) : 0;  // which P barrier pair
 #pragma unroll
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
@@ -528,7 +540,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + t));
+          if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + 2 * t + pSlot));
           if ((warp & 3) == 0) TFA_TR(t, it, 5 + 2 * half);
         }
         l += sum2.x + sum2.y;
@@ -614,7 +626,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // Issue helpers.  The tensor pipe overlaps at most one MMA with the issuing thread's next instructions, so
       // everything between two tcgen05.mma costs tensor time: per MMA there is one 32-bit add on a descriptor word.
       const int t = (warp != 12) ? 1 : 0;
-      const uint32_t qLo = kLoT | ((sQ + (uint32_t)t * C::kTileBytes) >> 4);
+      const uint32_t qLo0 = kLoT | ((sQ + (uint32_t)t * C::kQBufs * C::kTileBytes) >> 4);
+      uint32_t qLo = qLo0;  // Q buffer of the current item
       const uint32_t dRegion = tmem + (uint32_t)(t * C::kSRegion);
       const uint32_t dO = tmem + (uint32_t)(C::kOCol0 + t * HDP);
       auto issueQK = [&](int blk, uint32_t kAddr, int part) {  // part 0 / 1: first / second half of the k-steps
@@ -668,6 +681,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         Work w;
         if (!make_work<NT>(p, idx, w)) continue;
         const int n = (t < NT) ? w.nblk[t] : 0;
+        qLo = qLo0 + (uint32_t)((qc % C::kQBufs) * (C::kTileBytes >> 4));
         const bool dual = (NT == 2) && !C::kRot && w.nblk[0] > 0 && w.nblk[1] > 0;
         auto takeTurn = [&]() {
           if (!dual) return;
@@ -688,7 +702,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const uint32_t ph0 = (ld / NS) & 1;
           if (n > 0) {
             wait_bar(bar(kBarKvFull + s0), ph0, wc, 8);
-            wait_bar(bar(kBarQFull + t), qc & 1, wc, 9);
+            wait_bar(bar(kBarQFull + 2 * t + (qc % C::kQBufs)), (qc / C::kQBufs) & 1, wc, 9);
             ptx::tc_fence_after();
           }
           takeTurn();
@@ -696,7 +710,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             issueQK(it, sKV + s0 * C::kTileBytes, 0);
             issueQK(it, sKV + s0 * C::kTileBytes, 1);
             ptx::tc_commit(bar(kBarSFull + t));
-            if (n == 1) ptx::tc_commit(bar(kBarQEmpty + t));  // Q tile no longer needed
+            if (n == 1) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
           }
           passTurn();
           release(s0, ph0, n > 0);
@@ -720,15 +734,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
               ptx::tc_commit(bar(kBarSFull + t));
-              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + t));
+              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
             }
             if (j < n) {
               wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
               if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
-              wait_bar(bar(kBarP0Ready + t), blk & 1, wc, 11);
+              wait_bar(bar(kBarP0Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 11);
               ptx::tc_fence_after();
               issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
-              wait_bar(bar(kBarP1Ready + t), blk & 1, wc, 15);
+              wait_bar(bar(kBarP1Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 15);
               ptx::tc_fence_after();
               issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
               ptx::tc_commit(bar(kBarPvDone + t));
@@ -745,8 +759,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
             if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
             if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
-            spin_bar(bar(kBarP0Ready + t), blk & 1, wc, 11);
-            p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + t), blk & 1);
+            spin_bar(bar(kBarP0Ready + 2 * t), blk & 1, wc, 11);
+            p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + 2 * t), blk & 1);
           }
           takeTurn();
           // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
@@ -757,7 +771,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             TFA_TR(3, blk, t * 4 + 0);
             issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
             if (!p1Ready) {
-              spin_bar(bar(kBarP1Ready + t), blk & 1, wc, 15);
+              spin_bar(bar(kBarP1Ready + 2 * t), blk & 1, wc, 15);
               ptx::tc_fence_after();
             }
             TFA_TR(3, blk, t * 4 + 1);
@@ -768,7 +782,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               passTurn();
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
               ptx::tc_commit(bar(kBarSFull + t));
-              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + t));
+              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
               TFA_TR(3, blk, t * 4 + 3);
             } else {
               passTurn();
@@ -804,19 +818,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // finished; pulling them into L2 now shortens that exposed load at the item boundary.
 #pragma unroll
         for (int t = 0; t < NT; t++) {
-          if (w.nblk[t] == 0 || qc[t] == 0) continue;
+          if (w.nblk[t] == 0 || qc[t] == 0 || C::kQBufs > 1) continue;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_3d(&tmQ, a * 64, w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
         }
 #pragma unroll
         for (int t = 0; t < NT; t++) {
           if (w.nblk[t] == 0) continue;
-          if (qc[t] > 0) wait_bar(bar(kBarQEmpty + t), (qc[t] - 1) & 1, wc, 22);
-          ptx::mbar_arrive_expect_tx(bar(kBarQFull + t), C::kTileBytes);
+          // buffer qc % kQBufs was last used by item qc - kQBufs of this tile
+          const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;  // buffer and how often it was used before
+          if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
+          ptx::mbar_arrive_expect_tx(bar(kBarQFull + 2 * t + qb), C::kTileBytes);
+          const uint32_t qDst = sQ + (t * C::kQBufs + qb) * C::kTileBytes;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_3d(sQ + t * C::kTileBytes + a * kSubTileBytes, &tmQ, bar(kBarQFull + t), a * 64,
-                             w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
+            ptx::tma_load_3d(qDst + a * kSubTileBytes, &tmQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
+                             (int)(w.qRow0 + w.qlo[t]));
           }
           qc[t]++;
         }
