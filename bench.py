@@ -44,7 +44,7 @@ DEFAULT_WORKLOAD = "bf16_noncausal_b2_s4096_h32_d128"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (decode: batch-8 capture scaled by units processed; traffic grows in proportion to batch).
 NCU_TRAFFIC_BYTES = {
-    "bf16_noncausal_b2_s4096_h32_d128": 201429248 + 49005312,
+    "bf16_noncausal_b2_s4096_h32_d128": 201475328 + 46450432,
     "bf16_decode_b64_skv32768_h32_8_d128": int((1074021000 + 4879104) * 8),
     "bf16_decode_b8_skv32768_h32_8_d128": 1074021000 + 4879104,
 }

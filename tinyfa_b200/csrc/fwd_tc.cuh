@@ -760,7 +760,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
             if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
             spin_bar(bar(kBarP0Ready + 2 * t), blk & 1, wc, 11);
+#ifdef TFA_TURN_WHEN_ALL_READY
+            spin_bar(bar(kBarP1Ready + 2 * t), blk & 1, wc, 15);
+            p1Ready = true;
+#else
             p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + 2 * t), blk & 1);
+#endif
           }
           takeTurn();
           // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
