@@ -375,6 +375,20 @@ def test_fixed_len_guard_bands_partial_tiles():
         assert np.abs(O.float().cpu().numpy() - ref).max() <= 2e-2
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp32"])
+def test_rows_past_a_batch_entry_never_leak(dtype):
+    """Key blocks that straddle the end of a batch entry read zeros, not the next entry: NaN / Inf stored in the
+    NEXT batch entry's K and V must not reach this entry's output (the reference zero-fills out-of-range rows,
+    reference csrc/flash_attn/mma/memory.cuh:52-59)."""
+    dims = (3, 70, 200, 4, 2, 128)
+    Q, K, V = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in _fixed_inputs(dims, seed=13))
+    K[1], V[1] = float("nan"), float("inf")
+    O = tf.flash_attn_forward(Q, K, V, is_causal=False)
+    ref = ao.fixed(Q[:1].float().cpu().numpy(), K[:1].float().cpu().numpy(), V[:1].float().cpu().numpy(), False)
+    assert torch.isfinite(O[0]).all() and torch.isfinite(O[2]).all()
+    assert np.abs(O[:1].float().cpu().numpy() - ref).max() <= cases.MAXABS_TOL[dtype]
+
+
 @pytest.mark.parametrize("pack", [0, 1])
 def test_gqa_packing_modes_agree(pack):
     """Interleaving a KV group's Q heads into one tile is a scheduling choice, not a numerical one."""

@@ -273,8 +273,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // Per-CTA work description, computed identically by every role.
 struct Work {
-  long long qRow0;   // first row of this sequence in Q/O
+  long long qRow0;   // first row of this sequence in Q/O (flattened [rows, H, D] view, used for the O stores)
   long long kvRow0;  // first row of this sequence in K/V
+  // TMA coordinates.  Fixed length: tensors are described as [B, S, H, D], so rows past the end of a batch entry are
+  // zero-filled by TMA exactly like the reference zero-fills them (reference csrc/flash_attn/mma/memory.cuh:52-59).
+  // Packed variable length: one "batch entry" holding all rows; rows past a sequence end belong to the next sequence
+  // and are masked (K) or weighted by P = 0 (V).
+  int qRowTma, kvRowTma, batchTma;
   int sq, skv;
   int unit;          // Q head unit (packs 1 << packShift heads)
   int hkv;
@@ -298,11 +303,17 @@ __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
     w.sq = q1 - q0;
     w.kvRow0 = k0;
     w.skv = k1 - k0;
+    w.qRowTma = q0;
+    w.kvRowTma = k0;
+    w.batchTma = 0;
   } else {
     w.sq = p.seqLenQ;
     w.skv = p.seqLenKV;
     w.qRow0 = (long long)b * p.seqLenQ;
     w.kvRow0 = (long long)b * p.seqLenKV;
+    w.qRowTma = 0;
+    w.kvRowTma = 0;
+    w.batchTma = b;
   }
   const int rows = kBlockM >> p.packShift;  // sequence positions per tile
   const int seq0 = pairIdx * NT * rows;
@@ -825,7 +836,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int t = 0; t < NT; t++) {
           if (w.nblk[t] == 0 || qc[t] == 0 || C::kQBufs > 1) continue;
 #pragma unroll
-          for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_3d(&tmQ, a * 64, w.unit * gp, (int)(w.qRow0 + w.qlo[t]));
+          for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_4d(&tmQ, a * 64, w.unit * gp, w.qRowTma + w.qlo[t], w.batchTma);
         }
 #pragma unroll
         for (int t = 0; t < NT; t++) {
@@ -837,8 +848,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           const uint32_t qDst = sQ + (t * C::kQBufs + qb) * C::kTileBytes;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_3d(qDst + a * kSubTileBytes, &tmQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
-                             (int)(w.qRow0 + w.qlo[t]));
+            ptx::tma_load_4d(qDst + a * kSubTileBytes, &tmQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
+                             w.qRowTma + w.qlo[t], w.batchTma);
           }
           qc[t]++;
         }
@@ -849,10 +860,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           TFA_TR(4, i >> 1, (i & 1) * 2);
           ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
           const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
-          const int row = (int)(w.kvRow0 + (long long)(i >> 1) * kBlockN);
+          const int row = w.kvRowTma + (i >> 1) * kBlockN;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_3d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row);
+            ptx::tma_load_4d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row,
+                             w.batchTma);
           }
         }
       }

@@ -34,21 +34,23 @@ int device_num_sms(int device);       // c_abi.cu
 #define TFA_NAME(hdp, bf) TFA_CAT3(launch_fwd_tc_hdp##hdp, _bf, bf)
 #define TFA_NAME2(hdp, bf) TFA_NAME(hdp, bf)
 
-// rows x heads x headDim tensor, 16-bit elements; box = 64 elements x boxHeads x boxRows, 128-byte swizzle.
-static int make_map(CUtensorMap* m, const void* base, long long rows, int heads, int headDim, int boxHeads,
-                    int boxRows) {
+// [batches, rows, heads, headDim] tensor, 16-bit elements (packed varlen: batches = 1, rows = total);
+// box = 64 elements x boxHeads x boxRows x 1, 128-byte swizzle; out-of-range elements read as zero.
+static int make_map(CUtensorMap* m, const void* base, long long batches, long long rows, int heads, int headDim,
+                    int boxHeads, int boxRows) {
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) return kCudaError;
-  cuuint64_t dims[3] = {(cuuint64_t)headDim, (cuuint64_t)heads, (cuuint64_t)rows};
-  cuuint64_t strides[2] = {(cuuint64_t)headDim * 2, (cuuint64_t)heads * headDim * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)boxHeads, (cuuint32_t)boxRows};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(m, TFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  cuuint64_t dims[4] = {(cuuint64_t)headDim, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)batches};
+  cuuint64_t strides[3] = {(cuuint64_t)headDim * 2, (cuuint64_t)heads * headDim * 2,
+                           (cuuint64_t)rows * heads * headDim * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)boxHeads, (cuuint32_t)boxRows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, TFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_error_string("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld heads=%d headDim=%d box=%d,%d)",
-                     (int)r, rows, heads, headDim, boxHeads, boxRows);
+    set_error_string("cuTensorMapEncodeTiled failed with CUresult %d (batches=%lld rows=%lld heads=%d headDim=%d box=%d,%d)",
+                     (int)r, batches, rows, heads, headDim, boxHeads, boxRows);
     return kCudaError;
   }
   return kOk;
@@ -75,9 +77,12 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   const int rowsPerTile = tc::kBlockM >> packShift;
   CUtensorMap tmQ, tmK, tmV;
   int rc;
-  if ((rc = make_map(&tmQ, pr.Q, pr.totalQ, pr.headsQ, pr.headDim, gp, rowsPerTile)) != kOk) return rc;
-  if ((rc = make_map(&tmK, pr.K, pr.totalKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
-  if ((rc = make_map(&tmV, pr.V, pr.totalKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
+  const bool varlen = (pr.cuQ != nullptr);
+  const long long nb = varlen ? 1 : pr.batch;
+  const long long rowsQ = varlen ? pr.totalQ : pr.seqLenQ, rowsKV = varlen ? pr.totalKV : pr.seqLenKV;
+  if ((rc = make_map(&tmQ, pr.Q, nb, rowsQ, pr.headsQ, pr.headDim, gp, rowsPerTile)) != kOk) return rc;
+  if ((rc = make_map(&tmK, pr.K, nb, rowsKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
+  if ((rc = make_map(&tmV, pr.V, nb, rowsKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
 
   TcParams p;
   p.O = pr.O;

@@ -91,6 +91,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smemDst, const void* desc, 
       : "memory");
 }
 
+// 4-D tiled load global -> shared (head dim, head, row within the batch entry, batch entry).
+__device__ __forceinline__ void tma_load_4d(uint32_t smemDst, const void* desc, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smemDst), "l"(desc), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_4d(const void* desc, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];" ::"l"(desc), "r"(x), "r"(y), "r"(z),
+               "r"(w)
+               : "memory");
+}
+
 // Same box pulled into L2 only (no shared-memory destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_3d(const void* desc, int x, int y, int z) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(desc), "r"(x), "r"(y), "r"(z)
