@@ -176,6 +176,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank runs its own copy of the workload; strong: the ONE workload is split over the "
+                         "ranks by (batch x KV head) with tinyfa_b200.sharding.plan_fixed, outputs stay sharded")
+    ap.add_argument("--validate", action="store_true",
+                    help="strong scaling only: all-gather the sharded outputs once and compare with the unsharded result")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -211,7 +216,13 @@ def main():
     dt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype_name]
 
     decode = Sq == 1
-    g = torch.Generator().manual_seed(1234 + rank)
+    strong = args.scaling == "strong" and world > 1 and not decode
+    shard = None
+    if strong:
+        from tinyfa_b200 import sharding
+
+        shard = sharding.plan_fixed(B, Hkv, world)[rank]  # contiguous (batch, KV head) units of the ONE global problem
+    g = torch.Generator().manual_seed(1234 + (0 if strong else rank))
     if decode:
         # GBs of K/V: generated on the device; the end-to-end leg moves Q and O only (K/V are a resident cache)
         gd = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -220,10 +231,16 @@ def main():
         V = torch.randn(B, Skv, Hkv, D, generator=gd, device=dev, dtype=dt)
         host = [Q.cpu().pin_memory()]
     else:
-        host = [torch.randn(B, S, H, D, generator=g).to(dt).pin_memory() for S, H in ((Sq, Hq), (Skv, Hkv), (Skv, Hkv))]
+        full = [torch.randn(B, S, H, D, generator=g).to(dt) for S, H in ((Sq, Hq), (Skv, Hkv), (Skv, Hkv))]
+        if strong:
+            host = [t.pin_memory() for t in sharding.slice_fixed(full[0], full[1], full[2], shard)]
+        else:
+            host = [t.pin_memory() for t in full]
         Q, K, V = (t.to(dev) for t in host)
-    host_out = torch.empty(B, Sq, Hq, D, dtype=dt).pin_memory()
+        B, Hq, Hkv = Q.shape[0], Q.shape[2], K.shape[2]  # per-rank shapes from here on
+    globalB, globalHq, globalHkv = w[2], w[5], w[6]
 
+    host_out = torch.empty(B, Sq, Hq, D, dtype=dt).pin_memory()
     if args.impl == "ours":
         import tinyfa_b200 as tf
         from tinyfa_b200 import _lib
@@ -301,11 +318,30 @@ def main():
         if st != 0:
             raise RuntimeError(f"device status {st} site {site.value}")
 
-    fl = flops_of(w)
+    validation = None
+    if strong and args.validate and args.impl == "ours":
+        # the one collective of the design: gather the sharded outputs for a validation copy
+        o_local = step_api()
+        parts = [torch.empty_like(o_local) for _ in range(world)]
+        dist.all_gather(parts, o_local)
+        if rank == 0:
+            Qf, Kf, Vf = (t.to(dev) for t in full)
+            o_full = tf.flash_attn_forward(Qf, Kf, Vf, is_causal=causal)
+            glued = torch.empty_like(o_full)
+            for sh, part in zip(sharding.plan_fixed(globalB, globalHkv, world), parts):
+                sharding.place_fixed(glued, part, sh, globalHq // globalHkv)
+            validation = float((glued.float() - o_full.float()).abs().max().item())
+
+    fl = flops_of(w)  # the whole workload
     ms_step = ms_total / args.steps
-    value = world * fl / (ms_step * 1e-3) / 1e12
+    if strong:
+        value = fl / (ms_step * 1e-3) / 1e12          # total work fixed, split over the ranks
+        fl_kernel = fl / world                        # one rank's share
+    else:
+        value = world * fl / (ms_step * 1e-3) / 1e12  # every rank processed the whole workload
+        fl_kernel = fl
     peak, peak_src = measured_peak()
-    achieved = fl / (ms_kernel * 1e-3) / 1e12
+    achieved = fl_kernel / (ms_kernel * 1e-3) / 1e12
     esize = 2
     bytes_in = (B * Sq * Hq * D + 2 * B * Skv * Hkv * D) * esize
     bytes_out = B * Sq * Hq * D * esize
@@ -335,17 +371,23 @@ def main():
         line = {
             "metric": "attention fwd TFLOPS (bf16/fp16 hd128 seq4096)", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": dtype_name, "data": "synthetic",
             "config": {"workload": args.workload, "layout": "[B,S,H,D]", "causal": causal, "batch_per_gpu": B,
                        "seq_q": Sq, "seq_kv": Skv, "heads_q": Hq, "heads_kv": Hkv, "head_dim": D,
-                       "l2": "Q,K,V,O = 256 MiB per step > 126 MB L2; no flush", "per_gpu_tflops": value / world,
+                       "sharding": ("batch x KV head, %d units per rank, outputs sharded" % (shard.unit_end - shard.unit_begin))
+                       if strong else "replicas",
+                       "validation_max_abs_diff": validation,
+                       "l2": "Q,K,V,O = %d MiB per rank and step > 126 MB L2; no flush" % ((bytes_in + bytes_out) >> 20),
+                       "per_gpu_tflops": value / world,
                        "pct_of_nominal_2250": 100.0 * value / world / 2250.0},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if args.impl == "ours" else None,
                          "peak_source": peak_src,
                          "kernel_ms": ms_kernel},
-            "e2e": {"value": world * fl / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": bytes_in,
+            "e2e": {"value": (fl if strong else world * fl) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": bytes_in,
                     "d2h_bytes_per_step": bytes_out, "ms_per_step": ms_e2e},
             "gpu_launches": args.steps,
             "clocks": clocks,
