@@ -389,6 +389,21 @@ def test_rows_past_a_batch_entry_never_leak(dtype):
     assert np.abs(O[:1].float().cpu().numpy() - ref).max() <= cases.MAXABS_TOL[dtype]
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_host_tensor_entry_point_matches_device_path(causal):
+    """flash_attn_forward_host (pinned host tensors, pipelined copies) returns what flash_attn_forward returns."""
+    dims = (3, 1500, 1500, 8, 2, 128)
+    Q, K, V = (torch.from_numpy(x).to(torch.bfloat16) for x in _fixed_inputs(dims, seed=17))
+    Qp, Kp, Vp = Q.pin_memory(), K.pin_memory(), V.pin_memory()
+    out = tf.flash_attn_forward_host(Qp, Kp, Vp, is_causal=causal)
+    torch.cuda.synchronize()
+    expect = tf.flash_attn_forward(Q.cuda(), K.cuda(), V.cuda(), is_causal=causal).cpu()
+    assert out.is_pinned() and out.shape == Q.shape
+    assert (out.float() - expect.float()).abs().max().item() <= 2e-2
+    with pytest.raises(RuntimeError, match="CPU tensors"):
+        tf.flash_attn_forward_host(Q.cuda(), Kp, Vp)
+
+
 @pytest.mark.parametrize("pack", [0, 1])
 def test_gqa_packing_modes_agree(pack):
     """Interleaving a KV group's Q heads into one tile is a scheduling choice, not a numerical one."""

@@ -2,4 +2,6 @@
 from .api import (device_status, flash_attn_forward, flash_attn_varlen_forward, is_head_dim_compiled,
                   set_option)
 
-__all__ = ["flash_attn_forward", "flash_attn_varlen_forward", "is_head_dim_compiled", "device_status", "set_option"]
+from .host import flash_attn_forward_host
+
+__all__ = ["flash_attn_forward", "flash_attn_forward_host", "flash_attn_varlen_forward", "is_head_dim_compiled", "device_status", "set_option"]
