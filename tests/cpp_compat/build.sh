@@ -1,7 +1,7 @@
 #!/bin/sh
 # Builds the reference's OWN gtest suite and basic example, unchanged, against this library's drop-in header
 # (include/flash_attn/flash_api.cuh) and the small gtest stand-in beside this script.
-# Needs the reference checkout (REF, default /root/reference); outputs go to tests/cpp_compat/_build/ (git-ignored).
+# Needs the reference checkout (environment variable REF); outputs go to tests/cpp_compat/_build/ (git-ignored).
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
 ROOT="$(cd "$HERE/../.." && pwd)"
