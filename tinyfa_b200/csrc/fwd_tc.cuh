@@ -76,8 +76,19 @@ constexpr int kIssuerB = TFA_ISSUER_B;  // warp that issues the MMAs of Q tile 1
 #define TFA_SPECULATE 0
 #endif
 constexpr bool kSpeculate = TFA_SPECULATE != 0;
-constexpr int kEmuPeriod = 8;              // of every kEmuPeriod pairs of exponentials ...
+#ifndef TFA_EMU_PERIOD
+#define TFA_EMU_PERIOD 8
+#endif
+constexpr int kEmuPeriod = TFA_EMU_PERIOD;  // of every kEmuPeriod pairs of exponentials ...
 constexpr int kEmuCount = TFA_EMU_COUNT;   // ... this many are evaluated on the FMA pipe instead of the MUFU
+// Register split of the 64 K registers of an SM between the role groups (8 + 4 + 4 warps).
+#ifndef TFA_REGS_SOFTMAX
+#define TFA_REGS_SOFTMAX 176
+#endif
+constexpr int kRegsSoftmax = TFA_REGS_SOFTMAX;
+constexpr int kRegsEpilogue = (TFA_REGS_SOFTMAX == 176) ? 96 : (TFA_REGS_SOFTMAX == 184) ? 80 : (TFA_REGS_SOFTMAX == 192) ? 72 : 104;
+constexpr int kRegsIssue = (TFA_REGS_SOFTMAX == 192) ? 56 : (TFA_REGS_SOFTMAX == 168) ? 72 : 64;
+static_assert(8 * kRegsSoftmax + 4 * kRegsEpilogue + 4 * kRegsIssue <= 2048, "register budget (64 K registers / 32 lanes)");
 constexpr float kRescaleLog2 = 8.0f;  // lazy-rescale threshold, log2 units
 constexpr int kSubTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 16-bit elements), one swizzle-128B slab
 
@@ -414,7 +425,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   if (warp < 8) {
     // ================================================================ softmax
-    ptx::setmaxnreg_inc<176>();
+    ptx::setmaxnreg_inc<kRegsSoftmax>();
     const int t = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t tRegion = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(t * C::kSRegion);
@@ -493,9 +504,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         float mx4[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
+#ifdef TFA_MAX_8CHAINS
+          float ma = fmaxf(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
+          float mb = fmaxf(__uint_as_float(v[q][16]), __uint_as_float(v[q][17]));
+#pragma unroll
+          for (int i = 2; i < 16; i += 2) {
+            ma = fmax3(ma, __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
+            mb = fmax3(mb, __uint_as_float(v[q][16 + i]), __uint_as_float(v[q][17 + i]));
+          }
+          mx4[q] = fmaxf(ma, mb);
+#else
           mx4[q] = fmaxf(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
 #pragma unroll
           for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
+#endif
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         if ((warp & 3) == 0) TFA_TR(t, it, 2);
@@ -565,7 +587,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
   } else if (warp < 12) {
     // ================================================================ epilogue
-    ptx::setmaxnreg_dec<96>();
+    ptx::setmaxnreg_dec<kRegsEpilogue>();
     const int r = threadIdx.x & 127;
     const uint32_t laneOff = (uint32_t)((warp & 3) * 32) << 16;
     const int gp = 1 << p.packShift;
@@ -622,7 +644,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else {
-    ptx::setmaxnreg_dec<64>();
+    ptx::setmaxnreg_dec<kRegsIssue>();
     if ((warp == 12 || warp == kIssuerB) && lane == 0) {
       // ============================================================== MMA issue
       const int fmt = kBf16 ? 1 : 0;
