@@ -110,8 +110,14 @@ struct Cfg {
   // that the next S does not cover ([0,64) or [128,192)).  Q.K^T of block j+1 can then be issued as soon as the
   // softmax has read S of block j, instead of after P.V of block j: the softmax never waits for the tensor pipe.
   static constexpr bool kRot = (HDP == 64);
-  static constexpr int kSRegion = kRot ? 192 : 128;                       // columns per tile for S / P
-  static constexpr int kOCol0 = kRot ? 384 : ((kNT == 2) ? 256 : 128);
+  // HDP 192 / 256 run one Q tile per CTA, which leaves room for two full S buffers (columns [0,128) and [128,256)):
+  // Q.K^T of block j+1 is issued before P.V of block j and overlaps the softmax of block j.
+  static constexpr bool kDblS = (kNT == 1);
+  static constexpr bool kTwoPos = kRot || kDblS;                           // S / P alternate between two positions
+  static constexpr int kSPosStride = kRot ? 64 : (kDblS ? 128 : 0);        // column offset of S for odd blocks
+  static constexpr int kPPosStride = kTwoPos ? 128 : 0;                    // column offset of P for odd blocks
+  static constexpr int kSRegion = kRot ? 192 : (kDblS ? 256 : 128);        // columns per tile for S / P
+  static constexpr int kOCol0 = kRot ? 384 : 256;
   static constexpr int kSmemBytes = (kNT * kQBufs + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
 };
 
@@ -124,16 +130,16 @@ enum Bar : int {
   kBarQEmpty = 4,      // [tile][Q buffer]  last Q.K^T of the item finished: buffer may be overwritten (tcgen05.commit)
   kBarP0Ready = 8,     // [tile][S position] first half of P written (4 softmax warps; O already rescaled if needed)
   kBarP1Ready = 12,    // [tile][S position] second half of P written (4 softmax warps)
-  kBarSFull = 16,      // [2]  S = Q.K^T finished (tcgen05.commit)
-  kBarPvDone = 18,     // [2]  O += P.V finished (tcgen05.commit)
+  kBarSFull = 44,      // [tile][S position]  S = Q.K^T finished (tcgen05.commit)
+  kBarPvDone = 16,     // [tile][S position]  O += P.V finished (tcgen05.commit)
   kBarScaleFull = 20,  // [2]  softmax published the final row sums (once per tile and item)
   kBarTurn = 22,       // [2]  issue-turn token of the MMA thread of tile t
   kBarSFree = 24,      // [2]  softmax has read S into registers (rotating-S mode only)
   kBarOFree = 26,      // [2]  epilogue has read O of the item into registers (4 epilogue warps)
   kBarWorkFull = 28,   // [2]  loader published the next work item in slot k & 1
   kBarWorkEmpty = 30,  // [2]  every consumer has read the slot
-  kBarKvFull = 32,     // [kStages]
-  kBarKvEmpty = 40,    // [kStages]
+  kBarKvFull = 32,     // [kStages <= 6]
+  kBarKvEmpty = 38,    // [kStages <= 6]
   kNumBars = 48,
 };
 
@@ -357,7 +363,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   using C = Cfg<HDP>;
   constexpr int NT = C::kNT;
   constexpr int NS = C::kStages;
-  static_assert(NS <= 8, "barrier slots");
+  static_assert(NS <= 6, "barrier slots");
 
   extern __shared__ uint8_t smemRaw[];
   const uint32_t rawAddr = ptx::smem_u32(smemRaw);
@@ -379,11 +385,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ptx::mbar_init(bar(kBarQEmpty + 2 * t + u), 1);
         ptx::mbar_init(bar(kBarP0Ready + 2 * t + u), 4);
         ptx::mbar_init(bar(kBarP1Ready + 2 * t + u), 4);
+        ptx::mbar_init(bar(kBarSFull + 2 * t + u), 1);
+        ptx::mbar_init(bar(kBarPvDone + 2 * t + u), 1);
       }
-      ptx::mbar_init(bar(kBarSFull + t), 1);
       ptx::mbar_init(bar(kBarTurn + t), 1);
       ptx::mbar_init(bar(kBarSFree + t), 4);
-      ptx::mbar_init(bar(kBarPvDone + t), 1);
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
       ptx::mbar_init(bar(kBarOFree + t), 4);
       ptx::mbar_init(bar(kBarWorkFull + t), 1);
@@ -444,13 +450,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       float m = -INFINITY, l = 0.f;
       const int n = w.nblk[t];
       for (int j = 0; j < n; j++, it++) {
-        wait_bar(bar(kBarSFull + t), it & 1, wc, 1);
+        wait_bar(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)), (C::kTwoPos ? (it >> 1) : it) & 1, wc, 1);
         ptx::tc_fence_after();
         if ((warp & 3) == 0) TFA_TR(t, it, 0);
         uint32_t v[4][32];
-        const uint32_t tS = tRegion + (C::kRot ? (uint32_t)((it & 1) * 64) : 0u);   // S of this block
-        const uint32_t tP = tRegion + (C::kRot ? (uint32_t)((it & 1) * 128) : 0u);  // where its P goes
-        const int pSlot = C::kRot ? (it & 1) : 0;  // which P barrier pair
+        const uint32_t tS = tRegion + (uint32_t)((it & 1) * C::kSPosStride);   // S of this block
+        const uint32_t tP = tRegion + (uint32_t)((it & 1) * C::kPPosStride);   // where its P goes
+        const int pSlot = C::kTwoPos ? (it & 1) : 0;  // which P barrier pair
 #pragma unroll
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
@@ -533,7 +539,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           // phase in progress or the one just completed: P.V of block it-2 finished before S of this block was
           // produced, and P.V of this block cannot start before this warp arrives.)
           const float scale = grow ? ex2((m - mNew) * c) : 1.f;
-          wait_bar(bar(kBarPvDone + t), (it - 1) & 1, wc, 5);
+          wait_bar(bar(kBarPvDone + 2 * t + (C::kTwoPos ? ((it - 1) & 1) : 0)),
+                   (C::kTwoPos ? ((it - 1) >> 1) : (it - 1)) & 1, wc, 5);
           ptx::tc_fence_after();
           const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll 1
@@ -609,7 +616,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const float l = ctl->scale[t][r];
         // Last P.V of the item.  Valid as a parity wait: the softmax published its row sums after storing the
         // last P, i.e. after all earlier P.V of the tile, and the next item's P.V waits for kBarOFree below.
-        wait_bar(bar(kBarPvDone + t), (pvTotal[t] - 1) & 1, wc, 7);
+        // (with two S positions P.V of block X-1 may still be running at this point: its barrier is the other one)
+        const int lastBlk = pvTotal[t] - 1;
+        wait_bar(bar(kBarPvDone + 2 * t + (C::kTwoPos ? (lastBlk & 1) : 0)), (C::kTwoPos ? (lastBlk >> 1) : lastBlk) & 1, wc, 7);
         ptx::tc_fence_after();
         const float inv = (l > 0.f) ? (1.f / l) : 0.f;
         const int qpos = w.qlo[t] + (r >> p.packShift);
@@ -665,7 +674,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const uint32_t dO = tmem + (uint32_t)(C::kOCol0 + t * HDP);
       auto issueQK = [&](int blk, uint32_t kAddr, int part) {  // part 0 / 1: first / second half of the k-steps
         const uint32_t kLo = kLoT | (kAddr >> 4);
-        const uint32_t dS = dRegion + (C::kRot ? (uint32_t)((blk & 1) * 64) : 0u);
+        const uint32_t dS = dRegion + (uint32_t)((blk & 1) * C::kSPosStride);
 #pragma unroll
         for (int k2 = 0; k2 < HDP / 32; k2++) {
           const int kk = part * (HDP / 32) + k2;
@@ -675,7 +684,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       };
       auto issuePV = [&](int blk, uint32_t vAddr, uint32_t firstAcc, int half) {  // firstAcc: accumulate flag of k-step 0
         const uint32_t vLo = vLoT | (vAddr >> 4);
-        const uint32_t aP = dRegion + (C::kRot ? (uint32_t)((blk & 1) * 128) : 0u);
+        const uint32_t aP = dRegion + (uint32_t)((blk & 1) * C::kPPosStride);
 #pragma unroll
         for (int k4 = 0; k4 < kBlockN / 32; k4++) {
           const int kk = half * (kBlockN / 32) + k4;
@@ -715,7 +724,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!make_work<NT>(p, idx, w)) continue;
         const int n = (t < NT) ? w.nblk[t] : 0;
         qLo = qLo0 + (uint32_t)((qc % C::kQBufs) * (C::kTileBytes >> 4));
-        const bool dual = (NT == 2) && !C::kRot && w.nblk[0] > 0 && w.nblk[1] > 0;
+        const bool dual = (NT == 2) && !C::kTwoPos && w.nblk[0] > 0 && w.nblk[1] > 0;
         auto takeTurn = [&]() {
           if (!dual) return;
           if (t == 0) {
@@ -742,7 +751,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (n > 0) {
             issueQK(it, sKV + s0 * C::kTileBytes, 0);
             issueQK(it, sKV + s0 * C::kTileBytes, 1);
-            ptx::tc_commit(bar(kBarSFull + t));
+            ptx::tc_commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
             if (n == 1) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
           }
           passTurn();
@@ -750,23 +759,37 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ld++;
         }
         for (int j = 0; j < w.nmax; j++) {
-          const int sV = ld % NS;
-          const uint32_t phV = (ld / NS) & 1;
-          ld++;
           const bool hasNext = (j + 1 < w.nmax);
-          const int sK = ld % NS;
-          const uint32_t phK = (ld / NS) & 1;
+          // Ring order follows consumption order.  One S position: K0 | V0 K1 | V1 K2 | ...  Two S positions (the
+          // next scores are issued before P.V): K0 | K1 V0 | K2 V1 | ...
+          int sV, sK;
+          uint32_t phV, phK;
+          if constexpr (C::kTwoPos) {
+            sK = ld % NS;
+            phK = (ld / NS) & 1;
+            if (hasNext) ld++;
+            sV = ld % NS;
+            phV = (ld / NS) & 1;
+            ld++;
+          } else {
+            sV = ld % NS;
+            phV = (ld / NS) & 1;
+            ld++;
+            sK = ld % NS;
+            phK = (ld / NS) & 1;
+          }
           const int blk = it + j;  // running index of block j of this tile
-          if constexpr (C::kRot) {
-            // rotating S: the next scores first (they only wait for the softmax to have read the current ones),
-            // then P.V of the current block whenever its P arrives
+          if constexpr (C::kTwoPos) {
+            // two S positions: the next scores first (rotating S: they wait for the softmax to have read the
+            // current ones, whose columns they partly overwrite; two full buffers: the target buffer was last
+            // read by P.V of block j-1, issued earlier by this thread), then P.V of the current block
             if (j + 1 < n) {
               wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
-              wait_bar(bar(kBarSFree + t), blk & 1, wc, 18);
+              if constexpr (C::kRot) wait_bar(bar(kBarSFree + t), blk & 1, wc, 18);
               ptx::tc_fence_after();
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
-              ptx::tc_commit(bar(kBarSFull + t));
+              ptx::tc_commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
               if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
             }
             if (j < n) {
@@ -778,13 +801,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               wait_bar(bar(kBarP1Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 15);
               ptx::tc_fence_after();
               issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
-              ptx::tc_commit(bar(kBarPvDone + t));
+              ptx::tc_commit(bar(kBarPvDone + 2 * t + (blk & 1)));
             }
+            if (hasNext) release(sK, phK, j + 1 < n);
             release(sV, phV, j < n);
-            if (hasNext) {
-              release(sK, phK, j + 1 < n);
-              ld++;
-            }
             continue;
           }
           bool p1Ready = false;
@@ -819,13 +839,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
               passTurn();
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
-              ptx::tc_commit(bar(kBarSFull + t));
+              ptx::tc_commit(bar(kBarSFull + 2 * t));
               if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
               TFA_TR(3, blk, t * 4 + 3);
             } else {
               passTurn();
             }
-            ptx::tc_commit(bar(kBarPvDone + t));
+            ptx::tc_commit(bar(kBarPvDone + 2 * t));
           } else {
             passTurn();
           }
@@ -875,14 +895,31 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
           qc[t]++;
         }
-        const int numLoads = 2 * w.nmax;  // K0 V0 K1 V1 ...
+        const int numLoads = 2 * w.nmax;
         for (int i = 0; i < numLoads; i++, ld++) {
           const int s = ld % NS;
           if (ld >= NS) wait_bar(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, wc, 14);
           TFA_TR(4, i >> 1, (i & 1) * 2);
           ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
-          const CUtensorMap* tm = (i & 1) ? &tmV : &tmK;
-          const int row = w.kvRowTma + (i >> 1) * kBlockN;
+          bool isV;
+          int blkIdx;
+          if constexpr (C::kTwoPos) {  // K0 | K1 V0 | K2 V1 | ... | V(last)
+            if (i == 0) {
+              isV = false;
+              blkIdx = 0;
+            } else if (i == numLoads - 1) {
+              isV = true;
+              blkIdx = w.nmax - 1;
+            } else {
+              isV = (i & 1) == 0;
+              blkIdx = isV ? (i - 2) / 2 : (i + 1) / 2;
+            }
+          } else {  // K0 | V0 K1 | V1 K2 | ...
+            isV = (i & 1) != 0;
+            blkIdx = i >> 1;
+          }
+          const CUtensorMap* tm = isV ? &tmV : &tmK;
+          const int row = w.kvRowTma + blkIdx * kBlockN;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
             ptx::tma_load_4d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row,
