@@ -67,15 +67,6 @@ constexpr int kIssuerB = TFA_ISSUER_B;  // warp that issues the MMAs of Q tile 1
 #ifndef TFA_EMU_COUNT
 #define TFA_EMU_COUNT 1
 #endif
-#ifdef TFA_SPIN_SFULL
-#define TFA_SFULL_WAIT spin_bar
-#else
-#define TFA_SFULL_WAIT wait_bar
-#endif
-#ifndef TFA_SPECULATE
-#define TFA_SPECULATE 0
-#endif
-constexpr bool kSpeculate = TFA_SPECULATE != 0;
 #ifndef TFA_EMU_PERIOD
 #define TFA_EMU_PERIOD 8
 #endif
@@ -419,6 +410,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const WaitCtx wc{&ctl->failed, p.status, p.epoch};
 #ifdef TFA_TRACE
   const bool traceOn = (blockIdx.x == gridDim.x / 2) && lane == 0;
+  if (traceOn && warp == 14) {  // SM clock against wall clock over the life of this CTA
+    g_trace[(2 * kTraceIters + 0) * kTracePts + 0] = clock64();
+    g_trace[(2 * kTraceIters + 0) * kTracePts + 1] = ptx::global_timer_ns();
+  }
 #endif
 
   // Every consumer of work items (8 softmax warps, 4 epilogue warps, 2 MMA threads) reads item k from slot k & 1
@@ -460,6 +455,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int q = 0; q < 4; q++) ptx::tmem_ld_32x32b_x32(tS + q * 32, v[q]);
         ptx::tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 4; q++) ptx::tmem_ld_fence(v[q]);
         if constexpr (C::kRot) {  // S is in registers: the next Q.K^T may overwrite it
           ptx::tc_fence_before();
           __syncwarp();
@@ -498,32 +495,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             dst[i >> 1] = pack2<kBf16>(x.x, x.y);
           }
         };
-        // Optional speculation (off by default: measured slower): from the second block on, the first quarter's
-        // exponentials start against the OLD reference max while the row max of this block is still being reduced.
         uint32_t pkA[16], pkB[16];
-        float2 sumQ0 = make_float2(0.f, 0.f);
-        const bool spec = kSpeculate && (j > 0);
-        const float mUseOld = (m == -INFINITY) ? 0.f : m;
-        if (spec) expQuarter(v[0], -mUseOld * c, pkA, sumQ0);
 
         // row max: four independent chains of 3-input max
         float mx4[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-#ifdef TFA_MAX_8CHAINS
-          float ma = fmaxf(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
-          float mb = fmaxf(__uint_as_float(v[q][16]), __uint_as_float(v[q][17]));
-#pragma unroll
-          for (int i = 2; i < 16; i += 2) {
-            ma = fmax3(ma, __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
-            mb = fmax3(mb, __uint_as_float(v[q][16 + i]), __uint_as_float(v[q][17 + i]));
-          }
-          mx4[q] = fmaxf(ma, mb);
-#else
           mx4[q] = fmaxf(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
 #pragma unroll
           for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
-#endif
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         if ((warp & 3) == 0) TFA_TR(t, it, 2);
@@ -548,6 +528,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             uint32_t o[32];
             ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
             ptx::tmem_wait_ld();
+            ptx::tmem_ld_fence(o);
 #pragma unroll
             for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
             ptx::tmem_st_32x32b_x32(tO + ch * 32, o);
@@ -561,14 +542,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if ((warp & 3) == 0) TFA_TR(t, it, 3);
 
         const float negMc = -mUse * c;
-        if (!spec || mUse != mUseOld) {
-          sumQ0 = make_float2(0.f, 0.f);
-          expQuarter(v[0], negMc, pkA, sumQ0);
-        }
-        float2 sum2 = sumQ0;
+        float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           if (half == 0) {
+            expQuarter(v[0], negMc, pkA, sum2);
             expQuarter(v[1], negMc, pkB, sum2);
           } else {
             expQuarter(v[2], negMc, pkA, sum2);
@@ -632,6 +610,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           uint32_t o[32];
           ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
           ptx::tmem_wait_ld();
+          ptx::tmem_ld_fence(o);
           if (ch == HDP / 32 - 1) {  // O is in registers: the next item's first P.V may overwrite the accumulator
             ptx::tc_fence_before();
             __syncwarp();
@@ -791,16 +770,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
               ptx::tc_commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
               if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
+              TFA_TR(3, blk, t * 4 + 3);
             }
             if (j < n) {
               wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
               if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
               wait_bar(bar(kBarP0Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 11);
               ptx::tc_fence_after();
+              TFA_TR(3, blk, t * 4 + 0);
               issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
               wait_bar(bar(kBarP1Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 15);
               ptx::tc_fence_after();
+              TFA_TR(3, blk, t * 4 + 1);
               issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
+              TFA_TR(3, blk, t * 4 + 2);
               ptx::tc_commit(bar(kBarPvDone + 2 * t + (blk & 1)));
             }
             if (hasNext) release(sK, phK, j + 1 < n);
@@ -813,12 +796,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (j + 1 < n) wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
             if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
             spin_bar(bar(kBarP0Ready + 2 * t), blk & 1, wc, 11);
-#ifdef TFA_TURN_WHEN_ALL_READY
-            spin_bar(bar(kBarP1Ready + 2 * t), blk & 1, wc, 15);
-            p1Ready = true;
-#else
             p1Ready = ptx::mbar_test_wait(bar(kBarP1Ready + 2 * t), blk & 1);
-#endif
           }
           takeTurn();
           // The token is passed on while a few MMAs of this turn are still to be issued: the other thread needs
@@ -932,6 +910,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   ptx::tc_fence_before();
   __syncthreads();
+#ifdef TFA_TRACE
+  if (traceOn && warp == 14) {
+    g_trace[(2 * kTraceIters + 0) * kTracePts + 2] = clock64();
+    g_trace[(2 * kTraceIters + 0) * kTracePts + 3] = ptx::global_timer_ns();
+  }
+#endif
   if (warp == 12) {
     if (*wc.failed) __nanosleep(200000);  // a wait gave up: let whatever is still in flight drain before freeing
     ptx::tc_fence_after();

@@ -141,6 +141,14 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Values loaded by tcgen05.ld are defined only after tcgen05.wait::ld, but the compiler sees no dependence between
+// the wait and the destination registers.  Passing the registers through an empty volatile asm placed after the
+// wait pins every later use behind it (volatile asm statements keep their order); it emits no instruction.
+template <int N>
+__device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; i++) asm volatile("" : "+r"(r[i]));
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // mbarrier arrives once every tcgen05.mma previously issued by this thread has completed.
