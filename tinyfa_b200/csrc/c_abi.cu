@@ -15,19 +15,38 @@
 #include <mutex>
 
 #include "../../include/tinyfa_b200.h"
+#include "build_config.cuh"
 #include "tfa_common.cuh"
 
 namespace tfa_b200 {
 
 // ---- instantiations (fwd_tc_inst.cu, one object per pair)
-int launch_fwd_tc_hdp64_bf0(const FwdProblem&, int);
-int launch_fwd_tc_hdp64_bf1(const FwdProblem&, int);
-int launch_fwd_tc_hdp128_bf0(const FwdProblem&, int);
-int launch_fwd_tc_hdp128_bf1(const FwdProblem&, int);
-int launch_fwd_tc_hdp192_bf0(const FwdProblem&, int);
-int launch_fwd_tc_hdp192_bf1(const FwdProblem&, int);
-int launch_fwd_tc_hdp256_bf0(const FwdProblem&, int);
-int launch_fwd_tc_hdp256_bf1(const FwdProblem&, int);
+// Only the (padded head dim, dtype) pairs selected at build time exist as objects.
+#define TFA_DECLARE_TC(HDP)                                                               \
+  int launch_fwd_tc_hdp##HDP##_bf0(const FwdProblem&, int);                               \
+  int launch_fwd_tc_hdp##HDP##_bf1(const FwdProblem&, int);                               \
+  static inline int tc_call_hdp##HDP(const FwdProblem& p, int packShift, bool bf16) {     \
+    (void)p; (void)packShift;                                                             \
+    if (bf16) {                                                                           \
+      if constexpr (TFA_HAVE_BF16) return launch_fwd_tc_hdp##HDP##_bf1(p, packShift);     \
+    } else {                                                                              \
+      if constexpr (TFA_HAVE_FP16) return launch_fwd_tc_hdp##HDP##_bf0(p, packShift);     \
+    }                                                                                     \
+    return kBadDtype;                                                                     \
+  }
+#if TFA_HAVE_HDP64
+TFA_DECLARE_TC(64)
+#endif
+#if TFA_HAVE_HDP128
+TFA_DECLARE_TC(128)
+#endif
+#if TFA_HAVE_HDP192
+TFA_DECLARE_TC(192)
+#endif
+#if TFA_HAVE_HDP256
+TFA_DECLARE_TC(256)
+#endif
+#undef TFA_DECLARE_TC
 
 // ---- split-KV path for short query blocks (fwd_decode.cu)
 bool splitkv_applicable(const FwdProblem& p);
@@ -139,6 +158,13 @@ int check_device() {
 
 static bool head_dim_ok(int d) { return d == 32 || d == 64 || d == 96 || d == 128 || d == 192 || d == 256; }
 
+// A (dtype, padded head dim) kernel that the build left out: same message style as an unsupported head dim.
+static int not_compiled(const FwdProblem& p) {
+  set_error_string("TinyFA: kernel for dtype code %d, headDim %d was not compiled into this library "
+                   "(TFA_TARGET_HEADDIM_<N> / TFA_TARGET_DTYPE build switches)", p.dtype, p.headDim);
+  return dtype_compiled(p.dtype) ? kBadHeadDim : kBadDtype;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int pick_pack_shift(const FwdProblem& p) {
@@ -195,17 +221,36 @@ static int dispatch(const FwdProblem& p) {
   switch (p.headDim) {
     case 32:
     case 64:
-      return bf ? launch_fwd_tc_hdp64_bf1(p, ps) : launch_fwd_tc_hdp64_bf0(p, ps);
+#if TFA_HAVE_HDP64
+      return tc_call_hdp64(p, ps, bf);
+#else
+      break;
+#endif
     case 96:
     case 128:
-      return bf ? launch_fwd_tc_hdp128_bf1(p, ps) : launch_fwd_tc_hdp128_bf0(p, ps);
+#if TFA_HAVE_HDP128
+      return tc_call_hdp128(p, ps, bf);
+#else
+      break;
+#endif
     case 192:
-      return bf ? launch_fwd_tc_hdp192_bf1(p, ps) : launch_fwd_tc_hdp192_bf0(p, ps);
+#if TFA_HAVE_HDP192
+      return tc_call_hdp192(p, ps, bf);
+#else
+      break;
+#endif
     case 256:
-      return bf ? launch_fwd_tc_hdp256_bf1(p, ps) : launch_fwd_tc_hdp256_bf0(p, ps);
+#if TFA_HAVE_HDP256
+      return tc_call_hdp256(p, ps, bf);
+#else
+      break;
+#endif
     default:
       return kBadHeadDim;
   }
+  (void)ps;
+  (void)bf;
+  return not_compiled(p);
 }
 
 int validate_common(const void* Q, const void* K, const void* V, void* O, int dtype, int batch, int sq, int skv,
@@ -216,6 +261,14 @@ int validate_common(const void* Q, const void* K, const void* V, void* O, int dt
   }
   if (!head_dim_ok(d)) {
     set_error_string("TinyFA: unsupported headDim: %d", d);
+    return kBadHeadDim;
+  }
+  if (!dtype_compiled(dtype)) {
+    set_error_string("TinyFA: dtype code %d was not compiled into this library (TFA_TARGET_DTYPE build switch)", dtype);
+    return kBadDtype;
+  }
+  if (!head_dim_compiled(d)) {
+    set_error_string("TinyFA: headDim %d was not compiled into this library (TFA_TARGET_HEADDIM_%d build switch)", d, d);
     return kBadHeadDim;
   }
   if (batch < 0 || sq < 0 || skv < 0 || hq <= 0 || hkv <= 0) {
@@ -326,7 +379,7 @@ extern "C" int tfa_b200_fwd_varlen(const void* Q, const void* K, const void* V, 
   return dispatch(p);
 }
 
-extern "C" int tfa_b200_head_dim_supported(int headDim) { return head_dim_ok(headDim) ? 1 : 0; }
+extern "C" int tfa_b200_head_dim_supported(int headDim) { return head_dim_compiled(headDim) ? 1 : 0; }
 
 extern "C" const char* tfa_b200_last_error_string(void) { return g_err; }
 

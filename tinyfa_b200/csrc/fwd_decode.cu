@@ -22,6 +22,7 @@
 #include <mutex>
 
 #include "../../include/tinyfa_b200.h"
+#include "build_config.cuh"
 #include "tfa_common.cuh"
 
 namespace tfa_b200 {
@@ -450,6 +451,7 @@ int launch(const FwdProblem& pr, int splits, float* partO, float* partLse) {
 bool splitkv_applicable(const FwdProblem& p) {
   if (p.dtype != kFp16 && p.dtype != kBf16) return false;
   if (p.headDim != 64 && p.headDim != 128 && p.headDim != 256) return false;
+  if (!dtype_compiled(p.dtype) || !head_dim_compiled(p.headDim)) return false;  // left out at build time
   const int group = p.headsQ / p.headsKV;
   return (long long)p.seqLenQ * group <= decode::kRows && p.seqLenKV >= 256;
 }
@@ -478,18 +480,29 @@ int launch_fwd_splitkv(const FwdProblem& p, int splits, float* scratch) {
   float* partO = scratch;
   float* partLse = scratch ? scratch + (size_t)splits * rows * p.headDim : nullptr;
   const bool bf = (p.dtype == kBf16);
+#define TFA_DECODE_CASE(D)                                                                   \
+  case D:                                                                                    \
+    if (bf) {                                                                                \
+      if constexpr (TFA_HAVE_BF16) return decode::launch<D, true>(p, splits, partO, partLse);  \
+    } else {                                                                                 \
+      if constexpr (TFA_HAVE_FP16) return decode::launch<D, false>(p, splits, partO, partLse); \
+    }                                                                                        \
+    return kBadDtype;
+  (void)bf; (void)partO; (void)partLse;
   switch (p.headDim) {
-    case 64:
-      return bf ? decode::launch<64, true>(p, splits, partO, partLse) : decode::launch<64, false>(p, splits, partO, partLse);
-    case 128:
-      return bf ? decode::launch<128, true>(p, splits, partO, partLse)
-                : decode::launch<128, false>(p, splits, partO, partLse);
-    case 256:
-      return bf ? decode::launch<256, true>(p, splits, partO, partLse)
-                : decode::launch<256, false>(p, splits, partO, partLse);
+#if TFA_HAVE_HD64
+    TFA_DECODE_CASE(64)
+#endif
+#if TFA_HAVE_HD128
+    TFA_DECODE_CASE(128)
+#endif
+#if TFA_HAVE_HD256
+    TFA_DECODE_CASE(256)
+#endif
     default:
       return kBadHeadDim;
   }
+#undef TFA_DECODE_CASE
 }
 
 }  // namespace tfa_b200

@@ -16,6 +16,7 @@
 
 #include <mutex>
 
+#include "build_config.cuh"
 #include "tfa_common.cuh"
 
 namespace tfa_b200 {
@@ -39,7 +40,7 @@ struct Fp32Params {
 namespace fp32 {
 
 constexpr int kThreads = 128;
-constexpr int kBC = 64;
+[[maybe_unused]] constexpr int kBC = 64;
 
 __device__ __forceinline__ void cp_async16(float* smemDst, const float* gmemSrc, bool valid) {
   const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smemDst));
@@ -309,22 +310,41 @@ int launch(const FwdProblem& pr) {
 }  // namespace fp32
 
 int launch_fwd_fp32(const FwdProblem& pr) {
+#if TFA_HAVE_FP32
   switch (pr.headDim) {
+#if TFA_HAVE_HD32
     case 32:
       return fp32::launch<32, 64>(pr);
+#endif
+#if TFA_HAVE_HD64
     case 64:
       return fp32::launch<64, 64>(pr);
+#endif
+#if TFA_HAVE_HD96
     case 96:
       return fp32::launch<96, 64>(pr);
+#endif
+#if TFA_HAVE_HD128
     case 128:
       return fp32::launch<128, 64>(pr);
+#endif
+#if TFA_HAVE_HD192
     case 192:
       return fp32::launch<192, 64>(pr);
+#endif
+#if TFA_HAVE_HD256
     case 256:
       return fp32::launch<256, 64>(pr);
+#endif
     default:
-      return kBadHeadDim;
+      break;
   }
+  set_error_string("TinyFA: fp32 kernel for headDim %d was not compiled into this library", pr.headDim);
+  return kBadHeadDim;
+#else
+  set_error_string("TinyFA: fp32 kernels were not compiled into this library (TFA_TARGET_DTYPE build switch)");
+  return kBadDtype;
+#endif
 }
 
 }  // namespace tfa_b200
