@@ -86,8 +86,11 @@ EncodeTiledFn get_encode_tiled() {
 }
 
 // One small block of ints per device, allocated on first use and kept for the life of the process:
-// word 0 is the status word, words 1..kWorkCounters are work counters of the persistent kernel (one per launch
-// in flight, picked by launch epoch and zeroed on the launch stream).
+// word 0 is the status word, followed by kWorkCounters (work, done) counter pairs of the persistent kernel.  A launch
+// takes the pair picked by its epoch; both counters are zero whenever no launch that uses them is running, because
+// the last CTA of a launch to finish puts them back to zero (no memset on the launch path).  Launches on one stream
+// can therefore share a pair; launches that run at the same time need different pairs, which holds while fewer than
+// kWorkCounters launches are in flight.
 constexpr int kWorkCounters = 64;
 static std::mutex g_devMutex;
 static int* g_statusWord[64] = {nullptr};
@@ -98,8 +101,8 @@ int* device_status_word(int device) {
   if (device < 0 || device >= 64) return nullptr;
   if (g_statusWord[device] == nullptr) {
     int* p = nullptr;
-    if (cudaMalloc(&p, sizeof(int) * (1 + kWorkCounters)) != cudaSuccess ||
-        cudaMemset(p, 0, sizeof(int) * (1 + kWorkCounters)) != cudaSuccess) {
+    if (cudaMalloc(&p, sizeof(int) * (1 + 2 * kWorkCounters)) != cudaSuccess ||
+        cudaMemset(p, 0, sizeof(int) * (1 + 2 * kWorkCounters)) != cudaSuccess) {
       set_error_string("could not allocate the device status word: %s", cudaGetErrorString(cudaGetLastError()));
       return nullptr;
     }
@@ -108,16 +111,37 @@ int* device_status_word(int device) {
   return g_statusWord[device];
 }
 
-// Work counter for one launch: zeroed behind everything already enqueued on `stream`.
-int* device_work_counter(int device, int epoch, cudaStream_t stream) {
+// (work, done) counter pair for one launch; see above.
+int* device_work_counter(int device, int epoch) {
   int* base = device_status_word(device);
   if (base == nullptr) return nullptr;
-  int* counter = base + 1 + (epoch % kWorkCounters);
-  if (cudaMemsetAsync(counter, 0, sizeof(int), stream) != cudaSuccess) {
-    set_error_string("cudaMemsetAsync(work counter): %s", cudaGetErrorString(cudaGetLastError()));
-    return nullptr;
+  return base + 1 + 2 * (epoch % kWorkCounters);
+}
+
+// Stream-ordered scratch for the split-KV partials comes from a pool of this library's own, one per device, that
+// keeps its memory across synchronisations (release threshold = max): with the default pool every call that
+// follows a device synchronise would pay a fresh device allocation (~200 us, measured).
+static cudaMemPool_t g_scratchPool[64] = {nullptr};
+static cudaMemPool_t scratch_pool(int device) {
+  std::lock_guard<std::mutex> lock(g_devMutex);
+  if (device < 0 || device >= 64) return nullptr;
+  if (g_scratchPool[device] == nullptr) {
+    cudaMemPoolProps props;
+    memset(&props, 0, sizeof(props));
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device;
+    cudaMemPool_t pool = nullptr;
+    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    unsigned long long keep = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    g_scratchPool[device] = pool;
   }
-  return counter;
+  return g_scratchPool[device];
 }
 
 int device_num_sms(int device) {
@@ -195,7 +219,12 @@ static int dispatch_splitkv(const FwdProblem& p, int splits) {
   const size_t floats = splitkv_scratch_floats(p, splits);
   float* scratch = nullptr;
   if (floats > 0) {
-    cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&scratch), floats * sizeof(float), p.stream);
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaMemPool_t pool = scratch_pool(device);
+    cudaError_t e = (pool != nullptr)
+                        ? cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), floats * sizeof(float), pool, p.stream)
+                        : cudaMallocAsync(reinterpret_cast<void**>(&scratch), floats * sizeof(float), p.stream);
     if (e != cudaSuccess) {
       set_error_string("cudaMallocAsync(%zu bytes) for split-KV partials: %s", floats * sizeof(float),
                        cudaGetErrorString(e));

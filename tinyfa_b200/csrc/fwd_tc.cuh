@@ -48,7 +48,7 @@ struct TcParams {
   int numPairs;   // query tile pairs per sequence (from the maximum length)
   int numUnits;   // Q head units (headsQ >> packShift)
   int numWork;    // numPairs * numUnits * batch
-  int* workCounter;  // device counter, zero at launch: next work item
+  int* workCounter;  // device counters, zero at launch: [0] next work item, [1] CTAs that have finished
   int causal;
   float scaleLog2;  // log2(e) / sqrt(headDim)
   int* status;      // device status word
@@ -916,6 +916,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     g_trace[(2 * kTraceIters + 0) * kTracePts + 3] = ptx::global_timer_ns();
   }
 #endif
+  if (threadIdx.x == 0) {
+    // The last CTA to get here puts both counters back to zero for the next launch that uses them.  Every CTA's
+    // fetches from the work counter precede its arrival on the done counter (same CTA, separated by the barrier above).
+    __threadfence();
+    if (atomicAdd(p.workCounter + 1, 1) == (int)gridDim.x - 1) {
+      p.workCounter[0] = 0;
+      p.workCounter[1] = 0;
+    }
+  }
   if (warp == 12) {
     if (*wc.failed) __nanosleep(200000);  // a wait gave up: let whatever is still in flight drain before freeing
     ptx::tc_fence_after();

@@ -27,7 +27,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn get_encode_tiled();  // c_abi.cu
 int* device_status_word(int device);  // c_abi.cu: per-device status word (device memory)
 int next_epoch();                     // c_abi.cu
-int* device_work_counter(int device, int epoch, cudaStream_t stream);  // c_abi.cu
+int* device_work_counter(int device, int epoch);  // c_abi.cu
 int device_num_sms(int device);       // c_abi.cu
 
 #define TFA_CAT3(a, b, c) a##b##c
@@ -109,7 +109,7 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
     return kTooLarge;
   }
   p.numWork = (int)numWork;
-  p.workCounter = device_work_counter(device, p.epoch, pr.stream);
+  p.workCounter = device_work_counter(device, p.epoch);
   if (p.workCounter == nullptr) return kCudaError;
 
   // persistent: one CTA per SM (512 tensor-memory columns and ~200 KB of shared memory each)
