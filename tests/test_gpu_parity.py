@@ -418,6 +418,31 @@ def test_many_work_items_per_sm_are_repeatable(hd, causal):
     assert (first[5:].double() - ref).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("hd,causal", [(64, False), (128, False), (128, True), (256, False)])
+def test_running_max_jumps_between_key_blocks(hd, causal, dtype):
+    """Scores whose row maximum jumps by far more than 2^8 (in the exp2 domain) from one 128-key block to the next,
+    several times per row, next to rows whose maximum never moves: the accumulated O and row sum have to be moved
+    to the new reference maximum (the reference rescales on every block, reference
+    csrc/flash_attn/mma/softmax.cuh:67-111; the tensor-core kernel here does it only when the maximum outgrows a
+    threshold, so random inputs never reach that code)."""
+    B, S, H = 2, 640, 4
+    rng = np.random.default_rng(77)
+    Q = rng.normal(0, 1, (B, S, H, hd)).astype(np.float32)
+    K = rng.normal(0, 1, (B, S, H, hd)).astype(np.float32)
+    V = rng.uniform(-1, 1, (B, S, H, hd)).astype(np.float32)
+    K *= np.repeat(np.array([1.0, 6.0, 6.0, 36.0, 80.0], dtype=np.float32), 128)[None, :, None, None]
+    Q[:, 5::7] *= 1e-3     # every 7th query row: scores ~ 0 in every block, its maximum stays put
+    Q[:, 3::11] *= -1.0    # sign flips move which keys win, not the magnitudes
+    Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+    O = tf.flash_attn_forward(Qd, Kd, Vd, is_causal=causal)
+    out = O.float().cpu().numpy()
+    assert np.isfinite(out).all()
+    ref64 = ao.fixed(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), causal, "f64")
+    assert np.abs(out - ref64).max() <= cases.MAXABS_TOL[dtype]
+    tf.device_status()
+
+
 @pytest.mark.parametrize("pack", [0, 1])
 def test_gqa_packing_modes_agree(pack):
     """Interleaving a KV group's Q heads into one tile is a scheduling choice, not a numerical one."""

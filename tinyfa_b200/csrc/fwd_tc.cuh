@@ -79,7 +79,12 @@ constexpr int kEmuCount = TFA_EMU_COUNT;   // ... this many are evaluated on the
 constexpr int kRegsSoftmax = TFA_REGS_SOFTMAX;
 constexpr int kRegsEpilogue = (TFA_REGS_SOFTMAX == 176) ? 96 : (TFA_REGS_SOFTMAX == 184) ? 80 : (TFA_REGS_SOFTMAX == 192) ? 72 : 104;
 constexpr int kRegsIssue = (TFA_REGS_SOFTMAX == 192) ? 56 : (TFA_REGS_SOFTMAX == 168) ? 72 : 64;
-static_assert(8 * kRegsSoftmax + 4 * kRegsEpilogue + 4 * kRegsIssue <= 2048, "register budget (64 K registers / 32 lanes)");
+// setmaxnreg only moves registers between the warps of one CTA: what the softmax warps gain must have been given up
+// by the others, out of the allocation the CTA was launched with (registers per thread at launch = 64 K / threads,
+// rounded down to a multiple of 8).  An increase that cannot be served blocks for ever, so this is checked here.
+constexpr int kRegsAtLaunch = (65536 / kThreads) / 8 * 8;
+static_assert(8 * kRegsSoftmax + 4 * kRegsEpilogue + 4 * kRegsIssue <= (kThreads / 32) * kRegsAtLaunch,
+              "register budget: the CTA's launch allocation must cover every role's setmaxnreg value");
 constexpr float kRescaleLog2 = 8.0f;  // lazy-rescale threshold, log2 units
 constexpr int kSubTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 16-bit elements), one swizzle-128B slab
 
@@ -524,14 +529,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tc_fence_after();
           const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll 1
-          for (int ch = 0; ch < HDP / 32; ch++) {
-            uint32_t o[32];
-            ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
+          for (int ch = 0; ch < HDP / 16; ch++) {  // 16 columns at a time: the scores of this block stay in registers
+            uint32_t o[16];
+            ptx::tmem_ld_32x32b_x16(tO + ch * 16, o);
             ptx::tmem_wait_ld();
             ptx::tmem_ld_fence(o);
 #pragma unroll
-            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
-            ptx::tmem_st_32x32b_x32(tO + ch * 32, o);
+            for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+            ptx::tmem_st_32x32b_x16(tO + ch * 16, o);
           }
           ptx::tmem_wait_st();
           l *= scale;
