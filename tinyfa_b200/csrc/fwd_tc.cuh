@@ -155,12 +155,25 @@ __device__ unsigned long long g_trace[kTraceRoles * kTraceIters * kTracePts];
 
 constexpr int kWorkConsumers = 14;  // 8 softmax warps + 4 epilogue warps + 2 MMA-issuing threads
 
+// What the loader publishes about a work item: everything the other roles need, so that only one thread pays for
+// the divisions of make_work (and does so while the previous item is still being computed).
+struct WorkSlot {
+  int idx;         // work item index; negative: no more work
+  int sq, skv;
+  int unit;
+  long long qRow0;
+  int qlo[2];
+  int nblk[2];     // both zero: nothing to do for this index (tile pair past the end of a short sequence)
+  int nmax;
+  int pad;
+};
+
 struct Ctl {
   uint64_t bars[kNumBars];
   float scale[2][kBlockM];
   uint32_t tmemBase;
   int failed;
-  int work[2];
+  WorkSlot work[2];
 };
 
 struct WaitCtx {
@@ -423,10 +436,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   // Every consumer of work items (8 softmax warps, 4 epilogue warps, 2 MMA threads) reads item k from slot k & 1
   // and frees the slot; a negative index ends the loop.
-  auto fetchWork = [&](int k) -> int {
+  auto fetchWork = [&](int k, Work& w) -> int {
     wait_bar(bar(kBarWorkFull + (k & 1)), (k >> 1) & 1, wc, 20);
-    const int idx = *reinterpret_cast<volatile int*>(&ctl->work[k & 1]);
-    return idx;
+    const volatile WorkSlot* ws = &ctl->work[k & 1];
+    w.sq = ws->sq;
+    w.skv = ws->skv;
+    w.unit = ws->unit;
+    w.qRow0 = ws->qRow0;
+    w.qlo[0] = ws->qlo[0];
+    w.qlo[1] = ws->qlo[1];
+    w.nblk[0] = ws->nblk[0];
+    w.nblk[1] = ws->nblk[1];
+    w.nmax = ws->nmax;
+    return ws->idx;
   };
 
   if (warp < 8) {
@@ -439,12 +461,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     int it = 0;      // blocks of this tile processed so far, over all work items (phase of the per-block barriers)
     int items = 0;   // work items in which this tile was active
     for (int k = 0;; k++) {
-      const int idx = fetchWork(k);
+      Work w;
+      const int idx = fetchWork(k, w);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
       if (idx < 0 || *wc.failed) break;
-      Work w;
-      if (!make_work<NT>(p, idx, w)) continue;
+      if (w.nmax == 0) continue;
       if (t >= NT || w.nblk[t] == 0) continue;
       const int qpos = w.qlo[t] + (r >> p.packShift);
       float m = -INFINITY, l = 0.f;
@@ -584,12 +606,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     int items[2] = {0, 0};    // work items in which tile t was active
     int pvTotal[2] = {0, 0};  // blocks of tile t issued so far
     for (int k = 0;; k++) {
-      const int idx = fetchWork(k);
+      Work w;
+      const int idx = fetchWork(k, w);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
       if (idx < 0 || *wc.failed) break;
-      Work w;
-      if (!make_work<NT>(p, idx, w)) continue;
+      if (w.nmax == 0) continue;
 #pragma unroll
       for (int t = 0; t < NT; t++) {
         const int n = w.nblk[t];
@@ -678,17 +700,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
       // One issuing thread per Q tile (warp 12: tile 0, warp kIssuerB: tile 1).  Every wait and commit costs the
       // issuing thread ~100 clocks during which it feeds nothing to the tensor pipe; with two issuers the other
-      // tile's MMAs fill those gaps.  Both threads walk the same K0 V0 K1 V1 ... ring; a stage is released by one
-      // arrival per issuer (a tcgen05.commit when the tile used the block, a plain arrive when it did not).
-      // A thread that does not use a block still waits for it to land before releasing it: that keeps its
-      // arrivals in step with the loader, so two arrivals of one thread can never complete a phase on their own.
-      auto release = [&](int stage, uint32_t phase, bool used) {
-        if (used) {
-          ptx::tc_commit(bar(kBarKvEmpty + stage));
-        } else {
-          wait_bar(bar(kBarKvFull + stage), phase, wc, 13);
-          ptx::mbar_arrive(bar(kBarKvEmpty + stage));
-        }
+      // tile's MMAs fill those gaps.  Both threads walk the same ring of K/V loads; a stage is free again after two
+      // arrivals: a tcgen05.commit from each tile that used the block, and for a tile that did not use it (causal:
+      // the last block belongs to tile 1 alone; one-tile head dims: tile 1 never) one from the loader when it issues
+      // the load.  A thread therefore never waits for a block it does not need, and the loader's arrival cannot be
+      // counted for the stage's previous use because the loader has waited for that phase before re-using the stage.
+      auto release = [&](int stage, bool used) {
+        if (used) ptx::tc_commit(bar(kBarKvEmpty + stage));
       };
       // The two issuers take strict turns (A: tile 0, B: tile 1, A, B, ...), which keeps the two tiles in
       // anti-phase: one tile's softmax runs while the other tile's MMAs run.  Without the turn token the two
@@ -701,16 +719,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       int it = 0;    // blocks of this tile issued so far
       int qc = 0;    // work items in which this tile was active
       for (int k = 0;; k++) {
-        const int idx = fetchWork(k);
-        ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
-        if (idx < 0 || *wc.failed) break;
         Work w;
-        if (!make_work<NT>(p, idx, w)) continue;
+        const int idx = fetchWork(k, w);
+        ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
+        TFA_TR(2, k, t * 4 + 1);
+        if (idx < 0 || *wc.failed) break;
+        if (w.nmax == 0) continue;
         const int n = (t < NT) ? w.nblk[t] : 0;
         qLo = qLo0 + (uint32_t)((qc % C::kQBufs) * (C::kTileBytes >> 4));
         const bool dual = (NT == 2) && !C::kTwoPos && w.nblk[0] > 0 && w.nblk[1] > 0;
+        // The token covers the blocks both tiles have.  Past those (causal: tile 1 has one block more) the thread
+        // that still has work runs free and the other one moves on to the next item, whose first Q.K^T and softmax
+        // then overlap the last, unpaired block of this one instead of waiting behind it.
+        const int nTok = dual ? min(w.nblk[0], w.nblk[1]) : 0;
+        // The first Q.K^T of an item is issued without the token: tile 0 then starts the next item while tile 1 is
+        // still in the last block of this one, which also re-creates the phase offset between the tiles.
+        bool tok = false;
         auto takeTurn = [&]() {
-          if (!dual) return;
+          if (!tok) return;
           if (t == 0) {
             if (turn > 0) spin_bar(myTurn, (turn - 1) & 1, wc, 16);
           } else {
@@ -718,7 +744,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         };
         auto passTurn = [&]() {
-          if (dual) {
+          if (tok) {
             ptx::mbar_arrive(otherTurn);
             turn++;
           }
@@ -726,6 +752,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         {
           const int s0 = ld % NS;
           const uint32_t ph0 = (ld / NS) & 1;
+          TFA_TR(2, k, t * 4 + 2);
           if (n > 0) {
             wait_bar(bar(kBarKvFull + s0), ph0, wc, 8);
             wait_bar(bar(kBarQFull + 2 * t + (qc % C::kQBufs)), (qc / C::kQBufs) & 1, wc, 9);
@@ -735,11 +762,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (n > 0) {
             issueQK(it, sKV + s0 * C::kTileBytes, 0);
             issueQK(it, sKV + s0 * C::kTileBytes, 1);
+            TFA_TR(2, k, t * 4 + 3);
             ptx::tc_commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
             if (n == 1) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
           }
           passTurn();
-          release(s0, ph0, n > 0);
+          release(s0, n > 0);
           ld++;
         }
         for (int j = 0; j < w.nmax; j++) {
@@ -763,6 +791,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             phK = (ld / NS) & 1;
           }
           const int blk = it + j;  // running index of block j of this tile
+          tok = (j < nTok);
           if constexpr (C::kTwoPos) {
             // two S positions: the next scores first (rotating S: they wait for the softmax to have read the
             // current ones, whose columns they partly overwrite; two full buffers: the target buffer was last
@@ -791,8 +820,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               TFA_TR(3, blk, t * 4 + 2);
               ptx::tc_commit(bar(kBarPvDone + 2 * t + (blk & 1)));
             }
-            if (hasNext) release(sK, phK, j + 1 < n);
-            release(sV, phV, j < n);
+            if (hasNext) release(sK, j + 1 < n);
+            release(sV, j < n);
             continue;
           }
           bool p1Ready = false;
@@ -829,32 +858,63 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               passTurn();
             }
             ptx::tc_commit(bar(kBarPvDone + 2 * t));
+            TFA_TR(2, blk, t * 4 + 0);
           } else {
             passTurn();
           }
-          release(sV, phV, j < n);
+          release(sV, j < n);
+          TFA_TR(2, blk, t * 4 + 1);
           if (hasNext) {
-            release(sK, phK, j + 1 < n);
+            release(sK, j + 1 < n);
             ld++;
           }
+          TFA_TR(2, blk, t * 4 + 2);
         }
         it += n;
         if (n > 0) qc++;
+        TFA_TR(2, k + 1, t * 4 + 0);
       }
     } else if (warp == 13 && lane == 0) {
       // ============================================================== work distribution + TMA loads
       const int gp = 1 << p.packShift;
       int ld = 0;            // KV-ring loads issued so far
       int qc[2] = {0, 0};    // Q loads issued so far per tile
-      for (int k = 0;; k++) {
+      // Takes the next work index, works out its description and publishes both in slot k & 1 (free once every
+      // consumer has read item k - 2 from it).  Returns false when the work has run out.
+      Work wq[2];
+      bool valid[2];
+      auto publish = [&](int k) -> bool {
         if (k >= 2) wait_bar(bar(kBarWorkEmpty + (k & 1)), ((k >> 1) - 1) & 1, wc, 21);
         int idx = atomicAdd(p.workCounter, 1);
         if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
-        *reinterpret_cast<volatile int*>(&ctl->work[k & 1]) = idx;
-        ptx::mbar_arrive(bar(kBarWorkFull + (k & 1)));
-        if (idx < 0) break;
-        Work w;
-        if (!make_work<NT>(p, idx, w)) continue;
+        Work& w = wq[k & 1];
+        valid[k & 1] = (idx >= 0) && make_work<NT>(p, idx, w);
+        volatile WorkSlot* ws = &ctl->work[k & 1];
+        ws->idx = idx;
+        ws->sq = w.sq;
+        ws->skv = w.skv;
+        ws->unit = w.unit;
+        ws->qRow0 = w.qRow0;
+        ws->qlo[0] = w.qlo[0];
+        ws->qlo[1] = w.qlo[1];
+        ws->nblk[0] = valid[k & 1] ? w.nblk[0] : 0;
+        ws->nblk[1] = valid[k & 1] ? w.nblk[1] : 0;
+        ws->nmax = valid[k & 1] ? w.nmax : 0;
+        ptx::mbar_arrive(bar(kBarWorkFull + (k & 1)));  // release: the stores above are visible to whoever waits
+        TFA_TR(4, k, 4);
+        return idx >= 0;
+      };
+      bool more = publish(0);
+      for (int k = 0; more; k++) {
+        // Item k + 1 is taken and published two blocks before the end of this item's loads: by then this thread is
+        // only waiting for ring stages, and nobody waits for the atomic round trip and the divisions between two
+        // items.  (Doing it right after the first loads of the item, when the ring is still filling, cost 6 %.)
+        bool nextDone = false;
+        if (!valid[k & 1]) {
+          more = publish(k + 1);
+          continue;
+        }
+        const Work& w = wq[k & 1];
         // The Q tiles of this item cannot land in shared memory before the previous item's last Q.K^T has
         // finished; pulling them into L2 now shortens that exposed load at the item boundary.
 #pragma unroll
@@ -863,9 +923,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_4d(&tmQ, a * 64, w.unit * gp, w.qRowTma + w.qlo[t], w.batchTma);
         }
-#pragma unroll
-        for (int t = 0; t < NT; t++) {
-          if (w.nblk[t] == 0) continue;
+        auto loadQ = [&](int t) {
+          if (t >= NT || w.nblk[t] == 0) return;
           // buffer qc % kQBufs was last used by item qc - kQBufs of this tile
           const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;  // buffer and how often it was used before
           if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
@@ -877,12 +936,23 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                              w.qRowTma + w.qlo[t], w.batchTma);
           }
           qc[t]++;
-        }
+          TFA_TR(4, k, 5 + t);
+        };
+        // Order: Q of tile 0, the first K block, Q of tile 1, everything else.  Tile 0 finishes an item first (causal:
+        // one block earlier), so its Q buffer is free while tile 1 still computes; its first Q.K^T of this item then
+        // needs only these two loads and overlaps the end of the previous item.
+        loadQ(0);
         const int numLoads = 2 * w.nmax;
         for (int i = 0; i < numLoads; i++, ld++) {
+          if (i == 1) loadQ(1);
+          if (i == numLoads - 4 && !nextDone) {
+            more = publish(k + 1);
+            nextDone = true;
+          }
           const int s = ld % NS;
           if (ld >= NS) wait_bar(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, wc, 14);
           TFA_TR(4, i >> 1, (i & 1) * 2);
+          if (i == 0) TFA_TR(4, k, 7);
           ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
           bool isV;
           int blkIdx;
@@ -908,7 +978,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             ptx::tma_load_4d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row,
                              w.batchTma);
           }
+          // the stage-free arrival of every tile that will not touch this block
+#pragma unroll
+          for (int t = 0; t < 2; t++) {
+            if (t >= NT || blkIdx >= w.nblk[t]) ptx::mbar_arrive(bar(kBarKvEmpty + s));
+          }
         }
+        if (!nextDone) more = publish(k + 1);
       }
     }
   }
