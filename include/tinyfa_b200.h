@@ -83,7 +83,7 @@ const char* tfa_b200_version(void);
 /*
  * Allocation-free decode forward.  No counterpart in the reference (which has neither a split-KV path nor any
  * scratch memory).  Same tensors, layouts and result as tfa_b200_fwd, restricted to what the split-KV kernel
- * handles: fp16 / bf16, headDim 64 / 128 / 256, seqLenQ * (numHeadsQ / numHeadsKV) <= 16, seqLenKV >= 256.
+ * handles: fp16 / bf16, every supported headDim, seqLenQ * (numHeadsQ / numHeadsKV) <= 16, seqLenKV >= 256.
  *
  * For callers that cannot let a library allocate: engines that hand all device memory to their own planner at
  * start-up, and decode loops that must not risk a stalling or failing driver allocation.  tfa_b200_fwd keeps the

@@ -262,7 +262,9 @@ def test_config5b_decode_shape_bf16():
 
 @pytest.mark.parametrize("split", [-1, 1, 3, 0])
 @pytest.mark.parametrize("shape", [(2, 1, 700, 8, 2, 128, False), (2, 4, 1000, 8, 2, 128, True), (2, 2, 513, 16, 2, 64, False),
-                                   (1, 1, 2049, 4, 4, 256, False), (1, 3, 777, 5, 1, 128, True)])
+                                   (1, 1, 2049, 4, 4, 256, False), (1, 3, 777, 5, 1, 128, True),
+                                   (2, 1, 900, 8, 2, 32, False), (2, 2, 650, 12, 2, 96, True), (1, 1, 1300, 16, 2, 192, False),
+                                   (3, 1, 257, 4, 1, 96, False)])
 def test_short_query_split_kv_path(shape, split):
     """Short query blocks go through the split-KV kernel; every split count (and the tensor-core path, 0) agrees with fp64."""
     *dims, causal = shape

@@ -102,9 +102,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 // Byte offset of 16-byte chunk `c` of row `r` in a tile whose rows hold D 16-bit elements.
+// Rows are D * 2 bytes and contiguous, so which banks a row starts on depends on D: for D = 64, 128, 192, 256 every
+// row starts on bank 0 and chunk c is exchanged with c ^ (r & 7) (stays inside its group of eight chunks); for D = 32
+// and 96 (64- and 192-byte rows) rows alternate between the two halves of the 128-byte bank line and the chunk is
+// exchanged inside its group of four, c ^ ((r >> 1) & 3).  Either way the eight rows of an ldmatrix hit eight
+// different 16-byte bank groups.
 template <int D>
 __device__ __forceinline__ uint32_t swz(int r, int c) {
-  return (uint32_t)(r * (D * 2) + ((c ^ (r & 7)) << 4));
+  if constexpr (D == 32 || D == 96) {
+    return (uint32_t)(r * (D * 2) + ((c ^ ((r >> 1) & 3)) << 4));
+  } else {
+    return (uint32_t)(r * (D * 2) + ((c ^ (r & 7)) << 4));
+  }
 }
 
 // 64 keys x D of one KV head -> one stage; keys >= keyEnd are zero-filled.
@@ -450,7 +459,6 @@ int launch(const FwdProblem& pr, int splits, float* partO, float* partLse) {
 
 bool splitkv_applicable(const FwdProblem& p) {
   if (p.dtype != kFp16 && p.dtype != kBf16) return false;
-  if (p.headDim != 64 && p.headDim != 128 && p.headDim != 256) return false;
   if (!dtype_compiled(p.dtype) || !head_dim_compiled(p.headDim)) return false;  // left out at build time
   const int group = p.headsQ / p.headsKV;
   return (long long)p.seqLenQ * group <= decode::kRows && p.seqLenKV >= 256;
@@ -490,11 +498,20 @@ int launch_fwd_splitkv(const FwdProblem& p, int splits, float* scratch) {
     return kBadDtype;
   (void)bf; (void)partO; (void)partLse;
   switch (p.headDim) {
+#if TFA_HAVE_HD32
+    TFA_DECODE_CASE(32)
+#endif
 #if TFA_HAVE_HD64
     TFA_DECODE_CASE(64)
 #endif
+#if TFA_HAVE_HD96
+    TFA_DECODE_CASE(96)
+#endif
 #if TFA_HAVE_HD128
     TFA_DECODE_CASE(128)
+#endif
+#if TFA_HAVE_HD192
+    TFA_DECODE_CASE(192)
 #endif
 #if TFA_HAVE_HD256
     TFA_DECODE_CASE(256)
@@ -575,7 +592,7 @@ extern "C" int tfa_b200_fwd_decode_noalloc(const void* Q, const void* K, const v
   p.causal = isCausal ? 1 : 0;
   p.stream = static_cast<cudaStream_t>(stream);
   if (!splitkv_applicable(p)) {
-    set_error_string("tfa_b200_fwd_decode_noalloc handles fp16/bf16, headDim 64/128/256, seqLenQ * (Hq/Hkv) <= 16 and "
+    set_error_string("tfa_b200_fwd_decode_noalloc handles fp16/bf16, seqLenQ * (Hq/Hkv) <= 16 and "
                      "seqLenKV >= 256 only (got dtype %d, headDim %d, seqLenQ %d, group %d, seqLenKV %d)",
                      dtype, headDim, seqLenQ, numHeadsQ / numHeadsKV, seqLenKV);
     return kBadArgument;
