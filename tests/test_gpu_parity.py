@@ -445,6 +445,45 @@ def test_running_max_jumps_between_key_blocks(hd, causal, dtype):
     tf.device_status()
 
 
+def test_cuda_graph_capture_and_replay():
+    """The entry points only enqueue work on the caller's stream (no allocation, memset or synchronisation once the
+    per-device state exists), so a call can be captured into a CUDA graph and replayed: the persistent kernel's work
+    counters must be back at zero after every replay, and the allocation-free decode entry point must capture too."""
+    lib = _lib.load()
+    dims = (2, 640, 640, 8, 2, 128)
+    B, Sq, Skv, Hq, Hkv, D = dims
+    Q, K, V = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in _fixed_inputs(dims, seed=5))
+    O = torch.zeros_like(Q)
+    dq = Q[:, :1].contiguous()          # one query token per batch entry -> split-KV path
+    dO = torch.zeros_like(dq)
+    # first calls outside the capture: they create the per-device state (status word, counters, shared-memory opt-in)
+    assert lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), 2, B, Sq, Skv, Hq, Hkv, D, 1,
+                            torch.cuda.current_stream().cuda_stream) == 0
+    assert lib.tfa_b200_fwd_decode_noalloc(dq.data_ptr(), K.data_ptr(), V.data_ptr(), dO.data_ptr(), 2, B, 1, Skv, Hq,
+                                           Hkv, D, 0, 2, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    ref = O.clone()
+    dref = dO.clone()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            st = torch.cuda.current_stream().cuda_stream
+            rc1 = lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), 2, B, Sq, Skv, Hq, Hkv, D,
+                                   1, st)
+            rc2 = lib.tfa_b200_fwd_decode_noalloc(dq.data_ptr(), K.data_ptr(), V.data_ptr(), dO.data_ptr(), 2, B, 1,
+                                                  Skv, Hq, Hkv, D, 0, 2, st)
+    assert rc1 == 0 and rc2 == 0, _lib.last_error()
+    for _ in range(3):
+        O.zero_()
+        dO.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(O, ref) and torch.equal(dO, dref)
+    tf.device_status()
+
+
 @pytest.mark.parametrize("pack", [0, 1])
 def test_gqa_packing_modes_agree(pack):
     """Interleaving a KV group's Q heads into one tile is a scheduling choice, not a numerical one."""

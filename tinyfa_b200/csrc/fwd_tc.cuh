@@ -163,7 +163,7 @@ struct WorkSlot {
   int unit;
   long long qRow0;
   int qlo[2];
-  int nblk[2];     // both zero: nothing to do for this index (tile pair past the end of a short sequence)
+  int nblk[2];
   int nmax;
   int pad;
 };
@@ -882,13 +882,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // Takes the next work index, works out its description and publishes both in slot k & 1 (free once every
       // consumer has read item k - 2 from it).  Returns false when the work has run out.
       Work wq[2];
-      bool valid[2];
       auto publish = [&](int k) -> bool {
         if (k >= 2) wait_bar(bar(kBarWorkEmpty + (k & 1)), ((k >> 1) - 1) & 1, wc, 21);
-        int idx = atomicAdd(p.workCounter, 1);
-        if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
         Work& w = wq[k & 1];
-        valid[k & 1] = (idx >= 0) && make_work<NT>(p, idx, w);
+        // indices whose tile pair lies past the end of a short sequence (packed variable-length input) are
+        // dropped here: nobody else hears of them
+        int idx;
+        do {
+          idx = atomicAdd(p.workCounter, 1);
+          if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
+        } while (idx >= 0 && !make_work<NT>(p, idx, w));
         volatile WorkSlot* ws = &ctl->work[k & 1];
         ws->idx = idx;
         ws->sq = w.sq;
@@ -897,9 +900,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ws->qRow0 = w.qRow0;
         ws->qlo[0] = w.qlo[0];
         ws->qlo[1] = w.qlo[1];
-        ws->nblk[0] = valid[k & 1] ? w.nblk[0] : 0;
-        ws->nblk[1] = valid[k & 1] ? w.nblk[1] : 0;
-        ws->nmax = valid[k & 1] ? w.nmax : 0;
+        ws->nblk[0] = w.nblk[0];
+        ws->nblk[1] = w.nblk[1];
+        ws->nmax = w.nmax;
         ptx::mbar_arrive(bar(kBarWorkFull + (k & 1)));  // release: the stores above are visible to whoever waits
         TFA_TR(4, k, 4);
         return idx >= 0;
@@ -910,10 +913,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // only waiting for ring stages, and nobody waits for the atomic round trip and the divisions between two
         // items.  (Doing it right after the first loads of the item, when the ring is still filling, cost 6 %.)
         bool nextDone = false;
-        if (!valid[k & 1]) {
-          more = publish(k + 1);
-          continue;
-        }
         const Work& w = wq[k & 1];
         // The Q tiles of this item cannot land in shared memory before the previous item's last Q.K^T has
         // finished; pulling them into L2 now shortens that exposed load at the item boundary.
