@@ -8,6 +8,13 @@
  *
  * dtype codes (reference csrc/binding/flash_attn_binding.cu:22): 1 = fp16, 2 = bf16, 3 = fp32.
  * Every function returning int returns 0 on success or one of the TFA_B200_* codes.
+ *
+ * Streams and CUDA graphs: the first call on a device creates a few bytes of per-device state (a status word,
+ * work counters, shared-memory opt-in of the kernels, a scratch pool) with synchronous calls; make it outside a
+ * stream capture.  After that a forward call only enqueues kernels on `stream` (the split-KV path of tfa_b200_fwd
+ * also a stream-ordered allocation and free; tfa_b200_fwd_decode_noalloc none), so it can be captured into a
+ * CUDA graph and replayed; tfa_b200_fwd_varlen needs totalQ / totalKV >= 0 for that.  Launches that run at the
+ * same time on different streams are fine up to 64 in flight per device.
  */
 #ifndef TINYFA_B200_H_
 #define TINYFA_B200_H_
