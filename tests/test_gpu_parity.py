@@ -445,6 +445,40 @@ def test_running_max_jumps_between_key_blocks(hd, causal, dtype):
     tf.device_status()
 
 
+def test_concurrent_streams_do_not_share_state():
+    """Launches that overlap on different streams use different work-counter pairs and their own shared-memory
+    state: interleaving three streams (tensor-core, fp32 and split-KV paths) gives the same bits as running alone."""
+    lib = _lib.load()
+    shapes = [(2, (2, 1024, 1024, 8, 8, 128), 1), (2, (4, 777, 777, 4, 2, 64), 0), (3, (2, 300, 300, 4, 4, 64), 1),
+              (2, (8, 1, 2048, 16, 4, 128), 0)]
+    work = []
+    for code, dims, causal in shapes:
+        dt = {2: torch.bfloat16, 3: torch.float32}[code]
+        Q, K, V = (torch.from_numpy(x).to(dt).cuda() for x in _fixed_inputs(dims, seed=31))
+        alone = torch.zeros_like(Q)
+        B, Sq, Skv, Hq, Hkv, D = dims
+        assert lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), alone.data_ptr(), code, B, Sq, Skv, Hq, Hkv,
+                                D, causal, torch.cuda.current_stream().cuda_stream) == 0
+        work.append((code, dims, causal, Q, K, V, alone))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    bufs = [[torch.zeros_like(wk[3]) for wk in work] for _ in range(12)]
+    torch.cuda.synchronize()  # the zero-fills above ran on the default stream
+    outs = []
+    for rep in range(12):
+        for i, (code, dims, causal, Q, K, V, alone) in enumerate(work):
+            B, Sq, Skv, Hq, Hkv, D = dims
+            O = bufs[rep][i]
+            st = streams[(rep + i) % 3]
+            assert lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), code, B, Sq, Skv, Hq, Hkv,
+                                    D, causal, st.cuda_stream) == 0, _lib.last_error()
+            outs.append((O, alone))
+    torch.cuda.synchronize()
+    for O, alone in outs:
+        assert torch.equal(O, alone)
+    tf.device_status()
+
+
 def test_cuda_graph_capture_and_replay():
     """The entry points only enqueue work on the caller's stream (no allocation, memset or synchronisation once the
     per-device state exists), so a call can be captured into a CUDA graph and replayed: the persistent kernel's work
