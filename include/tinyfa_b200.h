@@ -14,7 +14,9 @@
  * stream capture.  After that a forward call only enqueues kernels on `stream` (the split-KV path of tfa_b200_fwd
  * also a stream-ordered allocation and free; tfa_b200_fwd_decode_noalloc none), so it can be captured into a
  * CUDA graph and replayed; tfa_b200_fwd_varlen needs totalQ / totalKV >= 0 for that.  Launches that run at the
- * same time on different streams are fine up to 64 in flight per device.
+ * same time on different streams are fine up to 64 in flight per device.  A captured call keeps the work-counter
+ * slot it was captured with: do not run two replays of the same captured call concurrently (replays that follow
+ * each other on one stream, the usual case, are fine).
  */
 #ifndef TINYFA_B200_H_
 #define TINYFA_B200_H_
