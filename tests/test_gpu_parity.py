@@ -445,6 +445,17 @@ def test_running_max_jumps_between_key_blocks(hd, causal, dtype):
     tf.device_status()
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp32_hd128_form_for_large_grids(causal):
+    """fp32 at head dim 128 switches to 128-row CTAs (256 threads) once the grid has at least three CTAs per SM;
+    the small fp32 cases above never get there.  Ragged lengths: the last Q tile and the last key block are partial."""
+    dims = (2, 1000, 1100, 32, 8, 128)   # ceil(1000 / 128) * 32 * 2 = 512 CTAs
+    Q, K, V = (torch.from_numpy(x).cuda() for x in _fixed_inputs(dims, seed=17))
+    O = tf.flash_attn_forward(Q, K, V, is_causal=causal)
+    ref = ao.fixed(Q.cpu().numpy(), K.cpu().numpy(), V.cpu().numpy(), causal, "f64")
+    assert np.abs(O.cpu().numpy() - ref).max() <= cases.MAXABS_TOL["fp32"]
+
+
 def test_concurrent_streams_do_not_share_state():
     """Launches that overlap on different streams use different work-counter pairs and their own shared-memory
     state: interleaving three streams (tensor-core, fp32 and split-KV paths) gives the same bits as running alone."""

@@ -6,8 +6,8 @@
 // "col >= seqLenKV" mask (fma/softmax.cuh:97-99), row sum 0 -> output 0 (fma/softmax.cuh:76),
 // sequences without keys leave O untouched (fma/kernel.cuh:116-119).
 //
-// One CTA (128 threads) owns BR query rows of one (batch, Q head) and streams 64-key blocks.
-// Thread (ty, tx) = (tid / 8, tid % 8) owns RPT = BR/16 rows; in S it owns the 8 columns tx + 8*i, in O
+// One CTA (2 * BR threads: 128 for BR = 64, 256 for BR = 128) owns BR query rows of one (batch, Q head) and streams
+// 64-key blocks.  Thread (ty, tx) = (tid / 8, tid % 8) owns RPT = 4 rows; in S it owns the 8 columns tx + 8*i, in O
 // the float4 chunks tx + 8*i of the head dim.  K and V blocks are staged with 16-byte cp.async into
 // padded rows (row stride D + 4 floats keeps the float4 reads of 8 neighbouring threads on distinct
 // banks); V(j) streams in under S(j) and K(j+1) under P.V(j).
@@ -20,6 +20,8 @@
 #include "tfa_common.cuh"
 
 namespace tfa_b200 {
+
+int device_num_sms(int device);  // c_abi.cu
 
 struct Fp32Params {
   const float* Q;
@@ -39,7 +41,7 @@ struct Fp32Params {
 
 namespace fp32 {
 
-constexpr int kThreads = 128;
+constexpr int kRowsPerThread = 4;
 [[maybe_unused]] constexpr int kBC = 64;
 
 __device__ __forceinline__ void cp_async16(float* smemDst, const float* gmemSrc, bool valid) {
@@ -77,11 +79,11 @@ constexpr bool use_packed_fma() {
   return D == 96 || D == 128 || D == 192;
 }
 
-template <int D, int ROWS, int LD>
+template <int D, int ROWS, int LD, int NTHREADS>
 __device__ __forceinline__ void load_tile(float* sm, const float* base, long long row0, long long rowEnd,
                                           long long rowStride) {
   constexpr int kChunks = ROWS * (D / 4);
-  for (int i = threadIdx.x; i < kChunks; i += kThreads) {
+  for (int i = threadIdx.x; i < kChunks; i += NTHREADS) {
     const int r = i / (D / 4), c = i % (D / 4);
     const bool valid = (row0 + r) < rowEnd;
     const float* src = base + (valid ? (row0 + r) : row0) * rowStride + c * 4;
@@ -90,10 +92,11 @@ __device__ __forceinline__ void load_tile(float* sm, const float* base, long lon
 }
 
 template <int D, int BR>
-__global__ void __launch_bounds__(kThreads) fwd_fp32_kernel(const Fp32Params p) {
+__global__ void __launch_bounds__(BR * 8 / kRowsPerThread) fwd_fp32_kernel(const Fp32Params p) {
+  constexpr int kThreads = BR * 8 / kRowsPerThread;
   constexpr int LD = D + 4;
   constexpr int LDP = kBC + 4;
-  constexpr int RPT = BR / 16;
+  constexpr int RPT = kRowsPerThread;
   constexpr int NCH = D / 32;
   extern __shared__ float4 smemF4[];
   float* sQ = reinterpret_cast<float*>(smemF4);
@@ -132,8 +135,8 @@ __global__ void __launch_bounds__(kThreads) fwd_fp32_kernel(const Fp32Params p) 
 
   const int ty = threadIdx.x >> 3, tx = threadIdx.x & 7;
 
-  load_tile<D, BR, LD>(sQ, gQ, qRow0 + q0, qRow0 + sq, qStride);
-  load_tile<D, kBC, LD>(sK, gK, kvRow0, kvRow0 + skv, kvStride);
+  load_tile<D, BR, LD, kThreads>(sQ, gQ, qRow0 + q0, qRow0 + sq, qStride);
+  load_tile<D, kBC, LD, kThreads>(sK, gK, kvRow0, kvRow0 + skv, kvStride);
   cp_async_commit();
 
   float o[RPT][NCH][4];
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(kThreads) fwd_fp32_kernel(const Fp32Params p) 
 
   for (int j = 0; j < nblk; j++) {
     const int kbase = j * kBC;
-    load_tile<D, kBC, LD>(sV, gV, kvRow0 + kbase, kvRow0 + skv, kvStride);
+    load_tile<D, kBC, LD, kThreads>(sV, gV, kvRow0 + kbase, kvRow0 + skv, kvStride);
     cp_async_commit();
     cp_async_wait<1>();  // Q and K(j) have landed
     __syncthreads();
@@ -256,7 +259,7 @@ __global__ void __launch_bounds__(kThreads) fwd_fp32_kernel(const Fp32Params p) 
     cp_async_wait<0>();  // V(j) has landed
     __syncthreads();     // ... and P is visible, and nobody still reads K(j)
     if (j + 1 < nblk) {
-      load_tile<D, kBC, LD>(sK, gK, kvRow0 + kbase + kBC, kvRow0 + skv, kvStride);
+      load_tile<D, kBC, LD, kThreads>(sK, gK, kvRow0 + kbase + kBC, kvRow0 + skv, kvStride);
     }
     cp_async_commit();
 
@@ -356,7 +359,7 @@ int launch(const FwdProblem& pr) {
   p.causal = pr.causal;
   p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)D));
   dim3 grid((unsigned)((pr.seqLenQ + BR - 1) / BR), (unsigned)pr.headsQ, (unsigned)pr.batch);
-  kernel<<<grid, kThreads, kSmem, pr.stream>>>(p);
+  kernel<<<grid, BR * 8 / kRowsPerThread, kSmem, pr.stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error_string("fp32 kernel launch failed: %s", cudaGetErrorString(e));
@@ -384,6 +387,15 @@ int launch_fwd_fp32(const FwdProblem& pr) {
 #endif
 #if TFA_HAVE_HD128
     case 128:
+      // The 64-row form fits one 4-warp CTA per SM only (119 KB of shared memory); with 128 rows and 256 threads an SM
+      // runs 8 warps and every K/V block serves twice as many rows: +18 % at B2 S4096 H32 (39 -> 46 TFLOP/s).  Small
+      // problems keep the 64-row form, which makes twice as many CTAs.
+      {
+        int device = 0;
+        cudaGetDevice(&device);
+        const long long ctas128 = (long long)((pr.seqLenQ + 127) / 128) * pr.headsQ * pr.batch;
+        if (ctas128 >= 3LL * device_num_sms(device)) return fp32::launch<128, 128>(pr);
+      }
       return fp32::launch<128, 64>(pr);
 #endif
 #if TFA_HAVE_HD192
