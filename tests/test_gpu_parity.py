@@ -391,6 +391,36 @@ def test_rows_past_a_batch_entry_never_leak(dtype):
     assert np.abs(O[:1].float().cpu().numpy() - ref).max() <= cases.MAXABS_TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16", "fp32"])
+@pytest.mark.parametrize("hd,causal", [(64, False), (128, False), (128, True), (256, False)])
+def test_packed_sequences_do_not_leak_into_each_other(hd, causal, dtype):
+    """Packed variable-length input: a key block that reaches past the end of a sequence holds the NEXT sequence's
+    rows.  NaN and Inf stored in that neighbour's K and V must not reach this sequence's output (the reference
+    zero-fills rows past a sequence end, reference csrc/flash_attn/mma/memory.cuh:52-59)."""
+    sq = [200, 300, 70, 129]
+    skv = [333, 130, 500, 64]
+    Hq, Hkv = 4, 2
+    Q, K, V, cu_q, cu_kv = _varlen_inputs(sq, skv, Hq, Hkv, hd)
+    Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+    # sequences 1 and 3 are poison; 0 and 2 must come out clean
+    for b in (1, 3):
+        Kd[cu_kv[b]:cu_kv[b + 1]] = float("nan")
+        Vd[cu_kv[b]:cu_kv[b + 1]] = float("inf")
+    cq, ck = torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_kv).cuda()
+    O = tf.flash_attn_varlen_forward(Qd, Kd, Vd, cq, ck, max(sq), max(skv), is_causal=causal)
+    Kc, Vc = Kd.clone(), Vd.clone()
+    for b in (1, 3):
+        Kc[cu_kv[b]:cu_kv[b + 1]] = 0
+        Vc[cu_kv[b]:cu_kv[b + 1]] = 0
+    ref = ao.varlen(Qd.float().cpu().numpy(), Kc.float().cpu().numpy(), Vc.float().cpu().numpy(), cu_q, cu_kv, causal,
+                    "f64")
+    out = O.float().cpu().numpy()
+    for b in (0, 2):
+        rows = slice(int(cu_q[b]), int(cu_q[b + 1]))
+        assert np.isfinite(out[rows]).all()
+        assert np.abs(out[rows] - ref[rows]).max() <= cases.MAXABS_TOL[dtype]
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_host_tensor_entry_point_matches_device_path(causal):
     """flash_attn_forward_host (pinned host tensors, pipelined copies) returns what flash_attn_forward returns."""

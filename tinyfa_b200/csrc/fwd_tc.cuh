@@ -314,16 +314,36 @@ struct Work {
   int nmax;
 };
 
+// Packed variable-length input, last key block of a sequence: overwrite the rows of the V tile that lie past the end
+// of the sequence with zeros (one thread per key row), once the tile has landed.  Kept out of line: it runs once per
+// sequence and tile, and inlined into the softmax loop it slows every other block down.
+template <int kSub>
+__device__ __noinline__ void zero_v_tail(uint32_t kvFullBar, uint32_t phase, const WaitCtx wc, uint32_t tileAddr, int row,
+                                         int tail) {
+  wait_bar(kvFullBar, phase, wc, 25);
+  if (row >= tail) {  // key rows [tail, 128) of the block are not this sequence's
+    const uint32_t rowAddr = tileAddr + (uint32_t)(row * 128);
+#pragma unroll
+    for (int a = 0; a < kSub; a++) {
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowAddr + a * kSubTileBytes + q * 16), "r"(0u) : "memory");
+      }
+    }
+  }
+  ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+}
+
 // Work item idx -> (query tile pair, Q head unit, batch entry); pair index fastest so that CTAs running at the
 // same time share K/V through L2, heavy (late) causal pairs of a head first.
-template <int NT>
+template <int NT, bool kVarlen>
 __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
   const int pr = idx % p.numPairs;
   const int rest = idx / p.numPairs;
   const int pairIdx = p.causal ? (p.numPairs - 1 - pr) : pr;
   w.unit = rest % p.numUnits;
   const int b = rest / p.numUnits;
-  if (p.cuQ != nullptr) {
+  if constexpr (kVarlen) {
     const int q0 = p.cuQ[b], q1 = p.cuQ[b + 1], k0 = p.cuKV[b], k1 = p.cuKV[b + 1];
     w.qRow0 = q0;
     w.sq = q1 - q0;
@@ -365,7 +385,9 @@ __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
 // Persistent kernel: gridDim.x CTAs (one per SM) pull work items from a global counter until it runs out, so the
 // prologue of the next item (Q/K/V loads, first Q.K^T) overlaps the epilogue of the current one.  Every mbarrier keeps
 // running across items; each role tracks phases with its own running counters.
-template <int HDP, bool kBf16>
+// kVarlen: packed variable-length input (cu_seqlens).  A separate instantiation, because even code that the
+// fixed-length path never executes costs it 4-5 % when it sits in the softmax loop (measured).
+template <int HDP, bool kBf16, bool kVarlen>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
@@ -460,6 +482,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const float c = p.scaleLog2;
     int it = 0;      // blocks of this tile processed so far, over all work items (phase of the per-block barriers)
     int items = 0;   // work items in which this tile was active
+    int ldBase = 0;  // K/V ring loads of all earlier items (packed variable-length input only, see below)
     for (int k = 0;; k++) {
       Work w;
       const int idx = fetchWork(k, w);
@@ -467,6 +490,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
       if (idx < 0 || *wc.failed) break;
       if (w.nmax == 0) continue;
+      const int ldItem = ldBase;
+      if constexpr (kVarlen) ldBase += 2 * w.nmax;
+      (void)ldItem;
       if (t >= NT || w.nblk[t] == 0) continue;
       const int qpos = w.qlo[t] + (r >> p.packShift);
       float m = -INFINITY, l = 0.f;
@@ -580,6 +606,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             expQuarter(v[3], negMc, pkB, sum2);
           }
           if ((warp & 3) == 0) TFA_TR(t, it, 4 + 2 * half);
+          if constexpr (kVarlen) {
+           if (half == 0 && kbase + kBlockN > w.skv) {
+            // Packed variable-length input: the rows of this V block past the end of the sequence are the next
+            // sequence's, and P = 0 times a NaN or Inf stored there would still poison O.  The reference zero-fills
+            // rows past a sequence end (reference csrc/flash_attn/mma/memory.cuh:52-59); here the softmax warps
+            // overwrite them with zeros in shared memory before they let P.V of this block start.  (Both tiles do
+            // it, each ahead of its own P.V; K needs nothing, its columns are masked whatever they hold.)
+            const int vi = C::kTwoPos ? ((j == w.nmax - 1) ? 2 * w.nmax - 1 : 2 * j + 2) : 2 * j + 1;  // ring order
+            const int ldv = ldItem + vi;
+            zero_v_tail<C::kSub>(bar(kBarKvFull + ldv % NS), (ldv / NS) & 1, wc,
+                                 sKV + (uint32_t)((ldv % NS) * C::kTileBytes), r, w.skv - kbase);
+           }
+          }
           ptx::tmem_st_32x32b_x16(tP + half * 32, pkA);
           ptx::tmem_st_32x32b_x16(tP + half * 32 + 16, pkB);
           ptx::tmem_wait_st();
@@ -891,7 +930,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         do {
           idx = atomicAdd(p.workCounter, 1);
           if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
-        } while (idx >= 0 && !make_work<NT>(p, idx, w));
+        } while (idx >= 0 && !make_work<NT, kVarlen>(p, idx, w));
         volatile WorkSlot* ws = &ctl->work[k & 1];
         ws->idx = idx;
         ws->sq = w.sq;

@@ -58,7 +58,8 @@ static int make_map(CUtensorMap* m, const void* base, long long batches, long lo
 
 int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   using C = tc::Cfg<TFA_HDP>;
-  auto kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0)>;
+  const bool varlen = (pr.cuQ != nullptr);
+  auto kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), true> : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), false>;
 
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return kCudaError;
@@ -66,7 +67,12 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   static cudaError_t attrErr[64];
   if (device < 0 || device >= 64) return kBadArgument;
   std::call_once(once[device], [&] {
-    attrErr[device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), false>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (attrErr[device] == cudaSuccess) {
+      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    }
   });
   if (attrErr[device] != cudaSuccess) {
     set_error_string("cudaFuncSetAttribute(%d bytes): %s", C::kSmemBytes, cudaGetErrorString(attrErr[device]));
@@ -77,7 +83,6 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   const int rowsPerTile = tc::kBlockM >> packShift;
   CUtensorMap tmQ, tmK, tmV;
   int rc;
-  const bool varlen = (pr.cuQ != nullptr);
   const long long nb = varlen ? 1 : pr.batch;
   const long long rowsQ = varlen ? pr.totalQ : pr.seqLenQ, rowsKV = varlen ? pr.totalKV : pr.seqLenKV;
   if ((rc = make_map(&tmQ, pr.Q, nb, rowsQ, pr.headsQ, pr.headDim, gp, rowsPerTile)) != kOk) return rc;
