@@ -385,15 +385,20 @@ __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
 // Persistent kernel: gridDim.x CTAs (one per SM) pull work items from a global counter until it runs out, so the
 // prologue of the next item (Q/K/V loads, first Q.K^T) overlaps the epilogue of the current one.  Every mbarrier keeps
 // running across items; each role tracks phases with its own running counters.
-// kVarlen: packed variable-length input (cu_seqlens).  A separate instantiation, because even code that the
-// fixed-length path never executes costs it 4-5 % when it sits in the softmax loop (measured).
-template <int HDP, bool kBf16, bool kVarlen>
+// kMode: 0 fixed length, 1 packed variable-length input (cu_seqlens), 2 fixed length where no score is ever masked
+// (not causal, key length a multiple of the 128-key block).  Separate instantiations, because code that a path never
+// executes still costs it when it sits in the softmax loop (measured: the variable-length code 4-5 % of the
+// fixed-length speed; the masking code 8 % at head dim 64 and nothing at 128 / 256, so mode 2 is only built for
+// the 64 kernel).
+constexpr int kModeFixed = 0, kModeVarlen = 1, kModeFixedNoMask = 2;
+template <int HDP, bool kBf16, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
   using C = Cfg<HDP>;
   constexpr int NT = C::kNT;
   constexpr int NS = C::kStages;
+  constexpr bool kVarlen = (kMode == kModeVarlen);
   static_assert(NS <= 6, "barrier slots");
 
   extern __shared__ uint8_t smemRaw[];
@@ -518,7 +523,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if ((warp & 3) == 0) TFA_TR(t, it, 1);
 
         const int kbase = j * kBlockN;
-        const bool needMask = (kbase + kBlockN > w.skv) || (p.causal && (kbase + kBlockN - 1 > w.qlo[t]));
+        const bool needMask = (kMode != kModeFixedNoMask) &&
+                              ((kbase + kBlockN > w.skv) || (p.causal && (kbase + kBlockN - 1 > w.qlo[t])));
         if (needMask) {
           int lim = w.skv - kbase;                         // columns [0, lim) are real keys
           if (p.causal) lim = min(lim, qpos - kbase + 1);  // ... that are not in the future

@@ -59,7 +59,14 @@ static int make_map(CUtensorMap* m, const void* base, long long batches, long lo
 int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   using C = tc::Cfg<TFA_HDP>;
   const bool varlen = (pr.cuQ != nullptr);
-  auto kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), true> : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), false>;
+  auto kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen>
+                       : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed>;
+#if TFA_HDP == 64
+  // nothing to mask: not causal, and the key length fills its last 128-key block
+  if (!varlen && !pr.causal && pr.seqLenKV % tc::kBlockN == 0) {
+    kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>;
+  }
+#endif
 
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return kCudaError;
@@ -67,12 +74,18 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   static cudaError_t attrErr[64];
   if (device < 0 || device >= 64) return kBadArgument;
   std::call_once(once[device], [&] {
-    attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), false>,
+    attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (attrErr[device] == cudaSuccess) {
-      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), true>,
+      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     }
+#if TFA_HDP == 64
+    if (attrErr[device] == cudaSuccess) {
+      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    }
+#endif
   });
   if (attrErr[device] != cudaSuccess) {
     set_error_string("cudaFuncSetAttribute(%d bytes): %s", C::kSmemBytes, cudaGetErrorString(attrErr[device]));
