@@ -9,14 +9,17 @@
  * dtype codes (reference csrc/binding/flash_attn_binding.cu:22): 1 = fp16, 2 = bf16, 3 = fp32.
  * Every function returning int returns 0 on success or one of the TFA_B200_* codes.
  *
- * Streams and CUDA graphs: the first call on a device creates a few bytes of per-device state (a status word,
- * work counters, shared-memory opt-in of the kernels, a scratch pool) with synchronous calls; make it outside a
- * stream capture.  After that a forward call only enqueues kernels on `stream` (the split-KV path of tfa_b200_fwd
- * also a stream-ordered allocation and free; tfa_b200_fwd_decode_noalloc none), so it can be captured into a
- * CUDA graph and replayed; tfa_b200_fwd_varlen needs totalQ / totalKV >= 0 for that.  Launches that run at the
- * same time on different streams are fine up to 64 in flight per device.  A captured call keeps the work-counter
- * slot it was captured with: do not run two replays of the same captured call concurrently (replays that follow
- * each other on one stream, the usual case, are fine).
+ * Streams and CUDA graphs: the first call on a device creates a few KB of per-device state (a status word, work
+ * counters and tensor-map slots, shared-memory opt-in of the kernels, a scratch pool) with synchronous calls; make it
+ * outside a stream capture.  After that a forward call only enqueues kernels on `stream` (the split-KV path of
+ * tfa_b200_fwd also a stream-ordered allocation and free; tfa_b200_fwd_decode_noalloc none), so it can be captured
+ * into a CUDA graph and replayed.  The persistent kernel hands out its work through a pair of device counters that two
+ * launches must not use at the same time: eager launches take the pair of their stream (up to 1024 distinct streams
+ * per device; the per-thread default stream counts once per calling thread), every captured launch takes a pair of
+ * its own for good (up to 3072 per device), past either limit the call returns TFA_B200_TOO_LARGE.  So eager launches
+ * on any streams and replays of captured graphs can run side by side; the one thing to avoid is instantiating one
+ * captured graph twice and running both executables at the same time.  Should two launches share a pair all the same,
+ * tfa_b200_device_status reports it (site 30).
  */
 #ifndef TINYFA_B200_H_
 #define TINYFA_B200_H_
@@ -52,9 +55,10 @@ int tfa_b200_fwd(const void* Q, const void* K, const void* V, void* O, int dtype
  *   Q, O : [totalQ, numHeadsQ, headDim]   K, V : [totalKV, numHeadsKV, headDim]
  *   cuSeqLensQ / cuSeqLensKV : int32 [batchSize + 1] prefix sums, DEVICE pointers.
  * maxSeqLenQ / maxSeqLenKV only size the launch, as in the reference (launcher.cuh:94-98).
- * totalQ / totalKV are the row counts of the packed tensors (= cuSeqLens[batchSize]); the reference
- * signature does not carry them, so a caller that only has the reference's arguments passes -1 and the
- * library then reads the two totals from the device with one stream-synchronising 8-byte copy.
+ * totalQ / totalKV are the row counts of the packed tensors (= cuSeqLens[batchSize]); the reference signature does
+ * not carry them, so a caller that only has the reference's arguments passes -1 for both.  The call stays
+ * asynchronous either way, as the reference's is (launcher.cuh:83-99): with -1 a one-warp kernel on `stream` reads the
+ * two totals from cuSeqLens on the device and completes the tensor maps there; nothing is copied back to the host.
  */
 int tfa_b200_fwd_varlen(const void* Q, const void* K, const void* V, void* O, const int* cuSeqLensQ,
                         const int* cuSeqLensKV, int dtype, int batchSize, int maxSeqLenQ, int maxSeqLenKV,
@@ -83,6 +87,9 @@ int tfa_b200_device_status(int* site);
  * at compile time (csrc/flash_attn/config.cuh:133-272).
  *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto / never / always
  *   "split_kv" -1/0/n  split-KV path for short query blocks (seqQ * group <= 16): auto / never / exactly n splits
+ *   "work_order" -1/0/n  order in which the persistent kernel hands out (query tile pair, head, batch) items:
+ *                      auto (causal: heaviest pairs first inside chunks of heads whose K/V fit a quarter of L2;
+ *                      otherwise pair index fastest) / pair index fastest / heaviest first in chunks of n heads
  * Returns TFA_B200_BAD_ARGUMENT for an unknown name.
  */
 int tfa_b200_set_option(const char* name, int value);

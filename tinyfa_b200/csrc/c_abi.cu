@@ -13,9 +13,12 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <thread>
+#include <unordered_map>
 
 #include "../../include/tinyfa_b200.h"
 #include "build_config.cuh"
+#include "ptx_sm100.cuh"
 #include "tfa_common.cuh"
 
 namespace tfa_b200 {
@@ -65,7 +68,10 @@ void set_error_string(const char* fmt, ...) {
 
 static std::atomic<int> g_optPackGqa{-1};
 static std::atomic<int> g_optSplitKv{-1};  // -1 auto, 0 never, n > 0 force n splits when applicable
+static std::atomic<int> g_optWorkOrder{-1};  // -1 auto, 0 pair index fastest, n > 0 heaviest first in chunks of n
 static std::atomic<int> g_epoch{1};
+
+int option_work_order() { return g_optWorkOrder.load(); }
 
 int next_epoch() { return (g_epoch.fetch_add(1) & 0x7FFFFF) + 1; }
 
@@ -85,37 +91,136 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
-// One small block of ints per device, allocated on first use and kept for the life of the process:
-// word 0 is the status word, followed by kWorkCounters (work, done) counter pairs of the persistent kernel.  A launch
-// takes the pair picked by its epoch; both counters are zero whenever no launch that uses them is running, because
-// the last CTA of a launch to finish puts them back to zero (no memset on the launch path).  Launches on one stream
-// can therefore share a pair; launches that run at the same time need different pairs, which holds while fewer than
-// kWorkCounters launches are in flight.
-constexpr int kWorkCounters = 64;
+// One small block of ints per device, allocated on first use and kept for the life of the process: word 0 is the
+// status word, followed by (work, done) counter pairs of the persistent kernel.  Both counters of a pair are zero
+// whenever no launch that uses them is running, because the last CTA of a launch to finish puts them back to zero
+// (no memset on the launch path).  Launches that may run at the same time must not share a pair, so:
+//   - an eager launch takes the pair of its stream (launches on one stream run one after the other); the per-thread
+//     default stream is one handle for many streams and is told apart by the calling thread;
+//   - a launch that is being captured into a CUDA graph takes a pair of its own that is never handed out again: the
+//     graph may later be replayed on any stream, next to anything.
+// kStreamPairs distinct streams and kCapturePairs captured launches per device are supported; past that the call
+// returns TFA_B200_TOO_LARGE instead of sharing a pair (two kernels on one pair would steal each other's work items).
+constexpr int kStreamPairs = 1024;
+constexpr int kCapturePairs = 3072;
 static std::mutex g_devMutex;
 static int* g_statusWord[64] = {nullptr};
 static int g_devChecked[64] = {0};  // 0 = unknown, 1 = cc 10.x, -1 = other
+struct StreamKey {
+  cudaStream_t stream;
+  std::thread::id thread;  // only for the per-thread default stream
+  bool operator==(const StreamKey& o) const { return stream == o.stream && thread == o.thread; }
+};
+struct StreamKeyHash {
+  size_t operator()(const StreamKey& k) const {
+    return std::hash<void*>()(static_cast<void*>(k.stream)) ^ (std::hash<std::thread::id>()(k.thread) * 1000003u);
+  }
+};
+static std::unordered_map<StreamKey, int, StreamKeyHash> g_streamPair[64];
+static int g_capturePairsUsed[64] = {0};
+// Beside every counter pair: room for three tensor maps (Q, K, V) that a launch completes on the device when the
+// host does not know the packed tensors' row totals (patch_varlen_maps below).  Same sharing rule as the counters.
+static CUtensorMap* g_mapBlock[64] = {nullptr};
 
-int* device_status_word(int device) {
-  std::lock_guard<std::mutex> lock(g_devMutex);
+static int* device_block_locked(int device) {
   if (device < 0 || device >= 64) return nullptr;
   if (g_statusWord[device] == nullptr) {
     int* p = nullptr;
-    if (cudaMalloc(&p, sizeof(int) * (1 + 2 * kWorkCounters)) != cudaSuccess ||
-        cudaMemset(p, 0, sizeof(int) * (1 + 2 * kWorkCounters)) != cudaSuccess) {
+    const size_t bytes = sizeof(int) * (1 + 2 * (kStreamPairs + kCapturePairs));
+    if (cudaMalloc(&p, bytes) != cudaSuccess || cudaMemset(p, 0, bytes) != cudaSuccess) {
       set_error_string("could not allocate the device status word: %s", cudaGetErrorString(cudaGetLastError()));
       return nullptr;
     }
+    CUtensorMap* maps = nullptr;
+    if (cudaMalloc(&maps, sizeof(CUtensorMap) * 3 * (kStreamPairs + kCapturePairs)) != cudaSuccess) {
+      set_error_string("could not allocate the device tensor-map block: %s", cudaGetErrorString(cudaGetLastError()));
+      cudaFree(p);
+      return nullptr;
+    }
     g_statusWord[device] = p;
+    g_mapBlock[device] = maps;
   }
   return g_statusWord[device];
 }
 
-// (work, done) counter pair for one launch; see above.
-int* device_work_counter(int device, int epoch) {
-  int* base = device_status_word(device);
-  if (base == nullptr) return nullptr;
-  return base + 1 + 2 * (epoch % kWorkCounters);
+int* device_status_word(int device) {
+  std::lock_guard<std::mutex> lock(g_devMutex);
+  return device_block_locked(device);
+}
+
+// (work, done) counter pair for one launch on `stream`; see above.  *rc receives the status when nullptr is returned.
+int* device_work_counter(int device, cudaStream_t stream, int* rc, CUtensorMap** maps) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+    set_error_string("cudaStreamIsCapturing: %s", cudaGetErrorString(cudaGetLastError()));
+    *rc = kCudaError;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_devMutex);
+  int* base = device_block_locked(device);
+  if (base == nullptr) {
+    *rc = kCudaError;
+    return nullptr;
+  }
+  if (cap != cudaStreamCaptureStatusNone) {
+    if (g_capturePairsUsed[device] >= kCapturePairs) {
+      set_error_string("more than %d launches of this library captured into CUDA graphs on device %d", kCapturePairs, device);
+      *rc = kTooLarge;
+      return nullptr;
+    }
+    const int slot = kStreamPairs + g_capturePairsUsed[device]++;
+    if (maps != nullptr) *maps = g_mapBlock[device] + 3 * slot;
+    return base + 1 + 2 * slot;
+  }
+  StreamKey key{stream, stream == cudaStreamPerThread ? std::this_thread::get_id() : std::thread::id()};
+  auto& table = g_streamPair[device];
+  auto it = table.find(key);
+  if (it == table.end()) {
+    if ((int)table.size() >= kStreamPairs) {
+      set_error_string("more than %d distinct streams used with this library on device %d", kStreamPairs, device);
+      *rc = kTooLarge;
+      return nullptr;
+    }
+    it = table.emplace(key, (int)table.size()).first;
+  }
+  if (maps != nullptr) *maps = g_mapBlock[device] + 3 * it->second;
+  return base + 1 + 2 * it->second;
+}
+
+// Completes the tensor maps of a packed variable-length launch on the device: the three maps arrive as kernel
+// arguments with a placeholder row count, the real counts are cuQ[batch] and cuKV[batch] (the reference reads its
+// lengths on the device as well, reference csrc/flash_attn/params.cuh:89-94).  One warp; the maps go to `out` in
+// global memory, from where the attention kernel of the same stream uses them.
+__global__ void patch_varlen_maps(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                                  const __grid_constant__ CUtensorMap mv, CUtensorMap* out, const int* cuQ,
+                                  const int* cuKV, int batch) {
+  __shared__ alignas(128) CUtensorMap sm[3];
+  const int lane = threadIdx.x;
+  const CUtensorMap* src[3] = {&mq, &mk, &mv};
+#pragma unroll
+  for (int i = 0; i < 3; i++) reinterpret_cast<uint32_t*>(&sm[i])[lane] = reinterpret_cast<const uint32_t*>(src[i])[lane];
+  __syncwarp();
+  if (lane == 0) {
+    const int rowsQ = cuQ[batch], rowsKV = cuKV[batch];
+    // an extent of zero is not a valid tensor map; with no rows the attention kernel finds no work and loads nothing
+    ptx::tensormap_set_dim2(ptx::smem_u32(&sm[0]), (uint32_t)(rowsQ > 0 ? rowsQ : 1));
+    ptx::tensormap_set_dim2(ptx::smem_u32(&sm[1]), (uint32_t)(rowsKV > 0 ? rowsKV : 1));
+    ptx::tensormap_set_dim2(ptx::smem_u32(&sm[2]), (uint32_t)(rowsKV > 0 ? rowsKV : 1));
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 3; i++) ptx::tensormap_publish(out + i, ptx::smem_u32(&sm[i]));
+}
+
+int launch_patch_varlen_maps(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, CUtensorMap* out,
+                             const int* cuQ, const int* cuKV, int batch, cudaStream_t stream) {
+  patch_varlen_maps<<<1, 32, 0, stream>>>(mq, mk, mv, out, cuQ, cuKV, batch);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error_string("tensor-map patch kernel launch failed: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  return kOk;
 }
 
 // Stream-ordered scratch for the split-KV partials comes from a pool of this library's own, one per device, that
@@ -373,18 +478,9 @@ extern "C" int tfa_b200_fwd_varlen(const void* Q, const void* K, const void* V, 
   }
   if ((rc = check_device()) != kOk) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (totalQ < 0 || totalKV < 0) {
-    int tq = 0, tkv = 0;
-    cudaError_t e = cudaMemcpyAsync(&tq, cuSeqLensQ + batchSize, sizeof(int), cudaMemcpyDeviceToHost, s);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(&tkv, cuSeqLensKV + batchSize, sizeof(int), cudaMemcpyDeviceToHost, s);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    if (e != cudaSuccess) {
-      set_error_string("reading cu_seqlens totals: %s", cudaGetErrorString(e));
-      return kCudaError;
-    }
-    totalQ = tq;
-    totalKV = tkv;
-  }
+  // Totals the caller does not know (the reference signature has none): the tensor-core path completes its tensor
+  // maps on the device from cu_seqlens[batch]; nothing is read back and the call stays asynchronous.
+  if (totalQ < 0 || totalKV < 0) totalQ = totalKV = -1;
   if (totalQ == 0 || totalKV == 0) return kOk;
   if (totalQ > 0x7FFFFFFFll || totalKV > 0x7FFFFFFFll) return kTooLarge;
   FwdProblem p;
@@ -432,7 +528,12 @@ extern "C" int tfa_b200_device_status(int* site) {
   if (v == 0) return kOk;
   cudaMemset(word, 0, sizeof(int));
   if (site != nullptr) *site = v & 0xFF;
-  set_error_string("a kernel gave up on a bounded wait (site %d, launch epoch %d)", v & 0xFF, v >> 8);
+  if ((v & 0xFF) == 30) {
+    set_error_string("two launches used one pair of work counters at the same time (launch epoch %d): results of both "
+                     "are incomplete", v >> 8);
+  } else {
+    set_error_string("a kernel gave up on a bounded wait (site %d, launch epoch %d)", v & 0xFF, v >> 8);
+  }
   return kDeviceTimeout;
 }
 
@@ -444,6 +545,10 @@ extern "C" int tfa_b200_set_option(const char* name, int value) {
   }
   if (strcmp(name, "split_kv") == 0) {
     g_optSplitKv.store(value < 0 ? -1 : value);
+    return kOk;
+  }
+  if (strcmp(name, "work_order") == 0) {
+    g_optWorkOrder.store(value < 0 ? -1 : value);
     return kOk;
   }
   set_error_string("unknown option '%s'", name);

@@ -158,8 +158,11 @@ __global__ void __launch_bounds__(kThreads) fwd_splitkv_kernel(const Params p) {
   const int nRows = sq * p.group;  // <= 16 by dispatch
   int keyEnd = skv;
   if (p.causal) keyEnd = min(keyEnd, sq);  // top-left causal: key j needs j <= i <= sq-1
+  // keysPerSplit comes from the caller's maximum key length, which only sizes the launch: the last split runs to
+  // the real end of the sequence, so an understated maximum loses no keys (the reference derives its key loop from
+  // the actual length as well, reference csrc/flash_attn/params.cuh:156-163).
   const int key0 = split * p.keysPerSplit;
-  const int key1 = min(key0 + p.keysPerSplit, keyEnd);
+  const int key1 = (split == p.splits - 1) ? keyEnd : min(key0 + p.keysPerSplit, keyEnd);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
 
@@ -373,6 +376,8 @@ __global__ void combine_kernel(const float* __restrict__ partO, const float* __r
   if (idx >= rows * (D / 4)) return;
   const long long row = idx / (D / 4);
   const int c4 = (int)(idx % (D / 4));
+  // packed input: rows past the last sequence (a Q tensor longer than cu_seqlens_q[batch]) have no partials
+  if (cuQ != nullptr && row / headsQ >= cuQ[batch]) return;
   float M = -INFINITY;
   for (int s = 0; s < splits; s++) M = fmaxf(M, partLse[(long long)s * rows + row]);
   if (M == -INFINITY) return;  // no keys at all for this row: leave O untouched
@@ -394,10 +399,7 @@ __global__ void combine_kernel(const float* __restrict__ partO, const float* __r
   out.x = pack2<kBf16>(acc.x * inv, acc.y * inv);
   out.y = pack2<kBf16>(acc.z * inv, acc.w * inv);
   *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(O) + row * D + c4 * 4) = out;
-  (void)cuQ;
   (void)cuKV;
-  (void)batch;
-  (void)headsQ;
 }
 
 template <int D, bool kBf16>
@@ -464,15 +466,22 @@ bool splitkv_applicable(const FwdProblem& p) {
   return (long long)p.seqLenQ * group <= decode::kRows && p.seqLenKV >= 256;
 }
 
-// Number of key-range splits: enough CTAs for two per SM (the kernel's occupancy), at least 256 keys per split.
-// Measured on the 8.6 GB decode shape (512 (batch, KV head) pairs): 1 split 7.1 TB/s, 2 splits 5.4, 8 splits 5.9.
+// Number of key-range splits.  The kernel runs two CTAs per SM; what costs time is a grid that is slightly larger than
+// a whole number of such waves (batch 8 x 8 KV heads with 5 splits = 320 CTAs on 296 slots: 256 us, with 4 or 8
+// splits 190 us), while splitting itself costs 20-25 % in partials and the combine pass once there are enough
+// (batch, KV head) pairs to fill the GPU without it (batch 64: 7.1 TB/s unsplit, 6.8 with 2-4 splits).  So: no split
+// from one full wave of pairs on, otherwise as many splits as fit two waves exactly or just under, at most 32
+// (measured at 32768 keys, 8 KV heads, batch 1 / 4 / 8 / 16: 60 / 121 / 196 / 331 us; best seen 60 / 114 / 188 / 331),
+// at least 256 keys per split.
 int splitkv_num_splits(const FwdProblem& p, int numSMs) {
   const long long base = (long long)p.batch * p.headsKV;
-  long long splits = (2LL * numSMs + base - 1) / base;
+  const long long slots = 2LL * numSMs;
+  if (base >= slots) return 1;
+  long long splits = (2 * slots) / base;
+  if (splits > 32) splits = 32;
   const long long maxSplits = (p.seqLenKV + 255) / 256;
   if (splits > maxSplits) splits = maxSplits;
   if (splits < 1) splits = 1;
-  if (splits > 128) splits = 128;
   return (int)splits;
 }
 

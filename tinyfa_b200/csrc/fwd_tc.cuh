@@ -48,10 +48,15 @@ struct TcParams {
   int numPairs;   // query tile pairs per sequence (from the maximum length)
   int numUnits;   // Q head units (headsQ >> packShift)
   int numWork;    // numPairs * numUnits * batch
+  int chunk;      // work index order: 0 = pair index fastest within a head; n > 0 = chunks of n (head unit, batch)
+                  // entries, inside a chunk the pair index slowest (see make_work)
   int* workCounter;  // device counters, zero at launch: [0] next work item, [1] CTAs that have finished
   int causal;
   float scaleLog2;  // log2(e) / sqrt(headDim)
   int* status;      // device status word
+  // packed variable-length input whose row totals the host does not know: the three tensor maps (Q, K, V), completed
+  // on the device by patch_varlen_maps from cuQ[batch] / cuKV[batch]; nullptr = use the maps passed as kernel arguments
+  const CUtensorMap* devMaps;
   int epoch;        // launch epoch (24 bits)
 };
 
@@ -60,25 +65,13 @@ namespace tc {
 constexpr int kBlockM = 128;  // query rows per tile = TMEM lanes
 constexpr int kBlockN = 128;  // keys per KV block
 constexpr int kThreads = 512;
-#ifndef TFA_ISSUER_B
-#define TFA_ISSUER_B 15
-#endif
-constexpr int kIssuerB = TFA_ISSUER_B;  // warp that issues the MMAs of Q tile 1
-#ifndef TFA_EMU_COUNT
-#define TFA_EMU_COUNT 1
-#endif
-#ifndef TFA_EMU_PERIOD
-#define TFA_EMU_PERIOD 8
-#endif
-constexpr int kEmuPeriod = TFA_EMU_PERIOD;  // of every kEmuPeriod pairs of exponentials ...
-constexpr int kEmuCount = TFA_EMU_COUNT;   // ... this many are evaluated on the FMA pipe instead of the MUFU
+constexpr int kIssuerB = 15;  // warp that issues the MMAs of Q tile 1 (warp 12 issues those of tile 0)
+constexpr int kEmuPeriod = 8;  // of every kEmuPeriod pairs of exponentials ...
+constexpr int kEmuCount = 1;   // ... this many are evaluated on the FMA pipe instead of the MUFU
 // Register split of the 64 K registers of an SM between the role groups (8 + 4 + 4 warps).
-#ifndef TFA_REGS_SOFTMAX
-#define TFA_REGS_SOFTMAX 176
-#endif
-constexpr int kRegsSoftmax = TFA_REGS_SOFTMAX;
-constexpr int kRegsEpilogue = (TFA_REGS_SOFTMAX == 176) ? 96 : (TFA_REGS_SOFTMAX == 184) ? 80 : (TFA_REGS_SOFTMAX == 192) ? 72 : 104;
-constexpr int kRegsIssue = (TFA_REGS_SOFTMAX == 192) ? 56 : (TFA_REGS_SOFTMAX == 168) ? 72 : 64;
+constexpr int kRegsSoftmax = 176;
+constexpr int kRegsEpilogue = 96;
+constexpr int kRegsIssue = 64;
 // setmaxnreg only moves registers between the warps of one CTA: what the softmax warps gain must have been given up
 // by the others, out of the allocation the CTA was launched with (registers per thread at launch = 64 K / threads,
 // rounded down to a multiple of 8).  An increase that cannot be served blocks for ever, so this is checked here.
@@ -93,13 +86,10 @@ struct Cfg {
   static constexpr int kSub = HDP / 64;                  // 64-element slabs per row
   static constexpr int kTileBytes = kSub * kSubTileBytes;  // one 128-row tile of Q, K or V
   static constexpr int kNT = (HDP <= 128) ? 2 : 1;       // Q tiles per CTA
-#ifndef TFA_QBUFS128
-#define TFA_QBUFS128 1
-#endif
   // Q buffers per tile: with two, the Q tiles of the next work item load while the current item still computes.
   // HDP == 128 would have to give up a K/V ring stage for that (227 KB of shared memory): measured 12 % slower.
-  static constexpr int kQBufs = (HDP == 64) ? 2 : (HDP == 128) ? TFA_QBUFS128 : 1;
-  static constexpr int kStages = (HDP == 64) ? 6 : (HDP == 128) ? (kQBufs == 2 ? 3 : 4) : (HDP == 192) ? 3 : 2;
+  static constexpr int kQBufs = (HDP == 64) ? 2 : 1;
+  static constexpr int kStages = (HDP == 64) ? 6 : (HDP == 128) ? 4 : (HDP == 192) ? 3 : 2;
   static constexpr int kTmemCols = 512;
   // HDP == 64 leaves tensor memory to spare, which buys a second S position per tile: S of block j sits at
   // columns [0,128) (j even) or [64,192) (j odd) of the tile's 192-column region and P of block j in the 64 columns
@@ -230,9 +220,16 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Row maximum with NaN kept (max.f32 would drop it): a NaN score must poison its row, as it does in the reference,
+// where it reaches the row sum through the exponential (reference csrc/flash_attn/mma/softmax.cuh:104-111).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float fmax2(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
   return d;
 }
 // two-wide fp32 FMA / ADD on a register pair
@@ -334,12 +331,27 @@ __device__ __noinline__ void zero_v_tail(uint32_t kvFullBar, uint32_t phase, con
   ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
 }
 
-// Work item idx -> (query tile pair, Q head unit, batch entry); pair index fastest so that CTAs running at the
-// same time share K/V through L2, heavy (late) causal pairs of a head first.
+// Work item idx -> (query tile pair, Q head unit, batch entry).  Two orders.  Pair index fastest: CTAs running at the
+// same time work on the same head and share its K/V through L2 (all items cost the same when nothing is causal).
+// Causal: the cost of an item grows with its pair index, so inside a chunk of p.chunk consecutive (head unit, batch)
+// entries the items are handed out heaviest first (pair index slowest, descending) - the longest-processing-time-first
+// rule, which leaves only light items for the end of the launch; neighbouring indices are then the Q heads of one KV
+// group, which still share K/V, and the host sizes the chunk so that the K/V of its heads stay resident in L2.
 template <int NT, bool kVarlen>
 __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
-  const int pr = idx % p.numPairs;
-  const int rest = idx / p.numPairs;
+  int pr, rest;
+  if (p.chunk > 0) {
+    const int per = p.numWork / p.numPairs;  // (head unit, batch) entries
+    const int chunkItems = p.chunk * p.numPairs;
+    const int c = idx / chunkItems;
+    const int within = idx - c * chunkItems;
+    const int width = min(p.chunk, per - c * p.chunk);  // the last chunk may be narrower
+    pr = within / width;
+    rest = c * p.chunk + (within - pr * width);
+  } else {
+    pr = idx % p.numPairs;
+    rest = idx / p.numPairs;
+  }
   const int pairIdx = p.causal ? (p.numPairs - 1 - pr) : pr;
   w.unit = rest % p.numUnits;
   const int b = rest / p.numUnits;
@@ -443,10 +455,27 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     ptx::tmem_alloc(ptx::smem_u32(&ctl->tmemBase), C::kTmemCols);
     ptx::tmem_relinquish();
   }
+  // tensor maps: the kernel arguments, or (packed input with totals only known on the device) maps in global memory
+  const CUtensorMap* mapQ = &tmQ;
+  const CUtensorMap* mapK = &tmK;
+  const CUtensorMap* mapV = &tmV;
+  if constexpr (kVarlen) {
+    if (p.devMaps != nullptr) {
+      mapQ = p.devMaps;
+      mapK = p.devMaps + 1;
+      mapV = p.devMaps + 2;
+    }
+  }
   if (warp == 13 && lane == 0) {
-    ptx::prefetch_tensormap(&tmQ);
-    ptx::prefetch_tensormap(&tmK);
-    ptx::prefetch_tensormap(&tmV);
+    if (kVarlen && p.devMaps != nullptr) {
+      ptx::tensormap_acquire(mapQ);
+      ptx::tensormap_acquire(mapK);
+      ptx::tensormap_acquire(mapV);
+    } else {
+      ptx::prefetch_tensormap(mapQ);
+      ptx::prefetch_tensormap(mapK);
+      ptx::prefetch_tensormap(mapV);
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -465,7 +494,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   // and frees the slot; a negative index ends the loop.
   auto fetchWork = [&](int k, Work& w) -> int {
     wait_bar(bar(kBarWorkFull + (k & 1)), (k >> 1) & 1, wc, 20);
-    const volatile WorkSlot* ws = &ctl->work[k & 1];
+    // plain loads: the barrier wait above is an acquire and a compiler-level memory fence, and fields that a role
+    // does not use cost it neither a load nor a register
+    const WorkSlot* ws = &ctl->work[k & 1];
     w.sq = ws->sq;
     w.skv = ws->skv;
     w.unit = ws->unit;
@@ -560,11 +591,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         float mx4[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-          mx4[q] = fmaxf(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
+          mx4[q] = fmax2(__uint_as_float(v[q][0]), __uint_as_float(v[q][1]));
 #pragma unroll
           for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float mx = fmax2(fmax2(mx4[0], mx4[1]), fmax2(mx4[2], mx4[3]));  // NaN if any score of the row is
         if ((warp & 3) == 0) TFA_TR(t, it, 2);
         // Lazy rescale: keep the old reference max while the new one exceeds it by less than kRescaleLog2 in
         // the exp2 domain (P then grows up to 2^kRescaleLog2, harmless in fp32 sums and 16-bit P); the
@@ -600,7 +631,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         m = mNew;
         if ((warp & 3) == 0) TFA_TR(t, it, 3);
 
-        const float negMc = -mUse * c;
+        // A NaN score makes every exponential of the row NaN (the pairs evaluated on the FMA pipe clamp their
+        // argument and would turn a NaN of their own into 0), hence the row sum and the output row.
+        const float negMc = (mx != mx) ? mx : -mUse * c;
         float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
@@ -924,6 +957,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const int gp = 1 << p.packShift;
       int ld = 0;            // KV-ring loads issued so far
       int qc[2] = {0, 0};    // Q loads issued so far per tile
+      bool pendQ[2] = {false, false};  // a Q load of tile t is noted but not issued yet (its buffer is still in use)
+      int pq[2][3];                    // ... and its coordinates: head, row, batch entry
       // Takes the next work index, works out its description and publishes both in slot k & 1 (free once every
       // consumer has read item k - 2 from it).  Returns false when the work has run out.
       Work wq[2];
@@ -965,36 +1000,85 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int t = 0; t < NT; t++) {
           if (w.nblk[t] == 0 || qc[t] == 0 || C::kQBufs > 1) continue;
 #pragma unroll
-          for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_4d(&tmQ, a * 64, w.unit * gp, w.qRowTma + w.qlo[t], w.batchTma);
+          for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_4d(mapQ, a * 64, w.unit * gp, w.qRowTma + w.qlo[t], w.batchTma);
         }
-        auto loadQ = [&](int t) {
-          if (t >= NT || w.nblk[t] == 0) return;
-          // buffer qc % kQBufs was last used by item qc - kQBufs of this tile
+        // Q loads never hold up the K/V stream.  A Q buffer is free only once the tile's last Q.K^T of the previous
+        // item has finished, which for tile 1 is a block later than for tile 0; a loader that waited for it in program
+        // order would keep the next item's first K/V blocks out of ring stages that are free already, and the tiles
+        // would start the item with nothing prefetched.  So a Q load is only noted here (pendQ) and issued from
+        // wherever this thread next polls, as soon as its buffer is free.
+        auto tryQ = [&](int t) -> bool {  // true: nothing pending for tile t (any more)
+          if (t >= NT || !pendQ[t]) return true;
           const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;  // buffer and how often it was used before
-          if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
+          if (qUse > 0 && !ptx::mbar_test_wait(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1)) return false;
           ptx::mbar_arrive_expect_tx(bar(kBarQFull + 2 * t + qb), C::kTileBytes);
           const uint32_t qDst = sQ + (t * C::kQBufs + qb) * C::kTileBytes;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_4d(qDst + a * kSubTileBytes, &tmQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
-                             w.qRowTma + w.qlo[t], w.batchTma);
+            ptx::tma_load_4d(qDst + a * kSubTileBytes, mapQ, bar(kBarQFull + 2 * t + qb), a * 64, pq[t][0], pq[t][1], pq[t][2]);
           }
           qc[t]++;
+          pendQ[t] = false;
           TFA_TR(4, k, 5 + t);
+          return true;
         };
-        // Order: Q of tile 0, the first K block, Q of tile 1, everything else.  Tile 0 finishes an item first (causal:
-        // one block earlier), so its Q buffer is free while tile 1 still computes; its first Q.K^T of this item then
-        // needs only these two loads and overlaps the end of the previous item.
-        loadQ(0);
+        // Wait for a barrier phase while a Q load is pending: suspended waits of at most 200 ns (no spinning: the
+        // warps that share this thread's scheduler need the issue slots), a look at the Q buffers in between.  With
+        // nothing pending it is the plain bounded wait.
+        auto waitWatchingQ = [&](uint32_t barAddr, uint32_t parity, int site) {
+          uint32_t rounds = 0;
+          uint64_t t0 = 0;
+          while (pendQ[0] || pendQ[1]) {
+            if (ptx::mbar_try_wait_ns(barAddr, parity, 200)) return;
+            tryQ(0);
+            tryQ(1);
+            if ((++rounds & 0x3F) == 0) {
+              if (*wc.failed) return;
+              const uint64_t now = ptx::global_timer_ns();
+              if (t0 == 0) {
+                t0 = now;
+              } else if (now - t0 > 2000000000ull) {
+                *wc.failed = 1;
+                atomicExch(wc.status, (wc.epoch << 8) | site);
+                return;
+              }
+            }
+          }
+          wait_bar(barAddr, parity, wc, site);
+        };
+        auto noteQ = [&](int t) {
+          if (t >= NT || w.nblk[t] == 0) return;
+          if (pendQ[t]) {  // the tile's previous Q load has to go out first (two items behind: rare)
+            const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;
+            if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
+            tryQ(t);
+          }
+          pq[t][0] = w.unit * gp;
+          pq[t][1] = w.qRowTma + w.qlo[t];
+          pq[t][2] = w.batchTma;
+          pendQ[t] = true;
+          tryQ(t);
+#ifdef TFA_X_NOPOLL
+          if (pendQ[t]) {
+            const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;
+            if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
+            tryQ(t);
+          }
+#endif
+        };
+        // Order when nothing has to wait: Q of tile 0, the first K block, Q of tile 1, everything else.  Tile 0 finishes
+        // an item first (causal: one block earlier), so its Q buffer is free while tile 1 still computes; its first
+        // Q.K^T of this item then needs only these two loads and overlaps the end of the previous item.
+        noteQ(0);
         const int numLoads = 2 * w.nmax;
         for (int i = 0; i < numLoads; i++, ld++) {
-          if (i == 1) loadQ(1);
+          if (i == 1) noteQ(1);
           if (i == numLoads - 4 && !nextDone) {
             more = publish(k + 1);
             nextDone = true;
           }
           const int s = ld % NS;
-          if (ld >= NS) wait_bar(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, wc, 14);
+          if (ld >= NS) waitWatchingQ(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, 14);
           TFA_TR(4, i >> 1, (i & 1) * 2);
           if (i == 0) TFA_TR(4, k, 7);
           ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
@@ -1015,7 +1099,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             isV = (i & 1) != 0;
             blkIdx = i >> 1;
           }
-          const CUtensorMap* tm = isV ? &tmV : &tmK;
+          const CUtensorMap* tm = isV ? mapV : mapK;
           const int row = w.kvRowTma + blkIdx * kBlockN;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
@@ -1029,6 +1113,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
         if (!nextDone) more = publish(k + 1);
+        if (!more) {  // last item: nothing may stay behind
+#pragma unroll
+          for (int t = 0; t < NT; t++) {
+            if (!pendQ[t]) continue;
+            const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;
+            if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 23);
+            tryQ(t);
+          }
+        }
       }
     }
   }
@@ -1046,6 +1139,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     // fetches from the work counter precede its arrival on the done counter (same CTA, separated by the barrier above).
     __threadfence();
     if (atomicAdd(p.workCounter + 1, 1) == (int)gridDim.x - 1) {
+      // Every CTA stops at its first index past the end, so the work counter must now read numWork + gridDim.x.
+      // Anything else means another launch used the same counters at the same time (the host hands out a pair per
+      // stream and per captured launch precisely to rule that out): report it rather than return a result with rows
+      // that nobody computed.
+      const int taken = *reinterpret_cast<volatile int*>(p.workCounter);
+      if (taken != p.numWork + (int)gridDim.x && *wc.failed == 0) atomicExch(p.status, (p.epoch << 8) | 30);
       p.workCounter[0] = 0;
       p.workCounter[1] = 0;
     }

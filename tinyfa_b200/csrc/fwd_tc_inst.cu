@@ -27,8 +27,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn get_encode_tiled();  // c_abi.cu
 int* device_status_word(int device);  // c_abi.cu: per-device status word (device memory)
 int next_epoch();                     // c_abi.cu
-int* device_work_counter(int device, int epoch);  // c_abi.cu
+int* device_work_counter(int device, cudaStream_t stream, int* rc, CUtensorMap** maps);  // c_abi.cu
+int launch_patch_varlen_maps(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, CUtensorMap* out,
+                             const int* cuQ, const int* cuKV, int batch, cudaStream_t stream);  // c_abi.cu
 int device_num_sms(int device);       // c_abi.cu
+int option_work_order();              // c_abi.cu: -1 auto, 0 pair index fastest, n > 0 chunk width
 
 #define TFA_CAT3(a, b, c) a##b##c
 #define TFA_NAME(hdp, bf) TFA_CAT3(launch_fwd_tc_hdp##hdp, _bf, bf)
@@ -97,7 +100,10 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   CUtensorMap tmQ, tmK, tmV;
   int rc;
   const long long nb = varlen ? 1 : pr.batch;
-  const long long rowsQ = varlen ? pr.totalQ : pr.seqLenQ, rowsKV = varlen ? pr.totalKV : pr.seqLenKV;
+  // packed input with unknown totals: placeholder extent, completed on the device before the kernel runs
+  const bool devMaps = varlen && (pr.totalQ < 0 || pr.totalKV < 0);
+  const long long rowsQ = varlen ? (devMaps ? 1 : pr.totalQ) : pr.seqLenQ;
+  const long long rowsKV = varlen ? (devMaps ? 1 : pr.totalKV) : pr.seqLenKV;
   if ((rc = make_map(&tmQ, pr.Q, nb, rowsQ, pr.headsQ, pr.headDim, gp, rowsPerTile)) != kOk) return rc;
   if ((rc = make_map(&tmK, pr.K, nb, rowsKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
   if ((rc = make_map(&tmV, pr.V, nb, rowsKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
@@ -127,8 +133,37 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
     return kTooLarge;
   }
   p.numWork = (int)numWork;
-  p.workCounter = device_work_counter(device, p.epoch);
-  if (p.workCounter == nullptr) return kCudaError;
+  // Causal problems: heaviest query tile pairs first inside chunks of (head unit, batch) entries.  A chunk is as wide
+  // as the KV heads whose K and V fit a quarter of the L2 (32 MB) together, and at least wide enough to hold two
+  // items per SM.  Option "work_order": -1 this rule, 0 pair index fastest, n > 0 chunks of n entries.
+  const int order = option_work_order();
+  p.chunk = 0;
+  if (order > 0) {
+    const long long per = (long long)p.numUnits * pr.batch;
+    p.chunk = (int)(order < per ? order : per);
+  } else if (order < 0 && pr.causal) {
+    const long long kvPerHead = 4ll * pr.seqLenKV * pr.headDim;  // K and V of one KV head, 16-bit elements
+    const int unitsPerKvHead = (p.group >> packShift) > 0 ? (p.group >> packShift) : 1;
+    long long heads = (32ll << 20) / (kvPerHead > 0 ? kvPerHead : 1);
+    if (heads < 1) heads = 1;
+    long long width = heads * unitsPerKvHead;
+    const long long minWidth = (2ll * device_num_sms(device) + p.numPairs - 1) / p.numPairs;
+    if (width < minWidth) width = minWidth;
+    const long long per = (long long)p.numUnits * pr.batch;
+    if (width > per) width = per;
+    // equal chunks: a narrow last chunk would start its heaviest items when everything else is about to finish
+    const long long chunks = (per + width / 2) / width > 0 ? (per + width / 2) / width : 1;
+    p.chunk = (int)((per + chunks - 1) / chunks);
+  }
+  int rcCounter = kCudaError;
+  CUtensorMap* slotMaps = nullptr;
+  p.workCounter = device_work_counter(device, pr.stream, &rcCounter, &slotMaps);
+  if (p.workCounter == nullptr) return rcCounter;
+  p.devMaps = nullptr;
+  if (devMaps) {
+    if ((rc = launch_patch_varlen_maps(tmQ, tmK, tmV, slotMaps, pr.cuQ, pr.cuKV, pr.batch, pr.stream)) != kOk) return rc;
+    p.devMaps = slotMaps;
+  }
 
   // persistent: one CTA per SM (512 tensor-memory columns and ~200 KB of shared memory each)
   const int ctas = (int)(numWork < device_num_sms(device) ? numWork : device_num_sms(device));

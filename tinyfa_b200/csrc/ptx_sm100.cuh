@@ -16,12 +16,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint32_t lane_id() {
-  uint32_t l;
-  asm volatile("mov.u32 %0, %%laneid;" : "=r"(l));
-  return l;
-}
-
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -57,6 +51,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with an upper bound (nanoseconds) on how long the thread may stay suspended: for a thread that watches
+// a second condition while it waits, without spinning on issue slots that the other warps of its scheduler need.
+__device__ __forceinline__ bool mbar_try_wait_ns(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Non-blocking probe of a phase (try_wait may suspend the thread and wake it up late).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -83,14 +93,6 @@ __device__ __forceinline__ void prefetch_tensormap(const void* desc) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(desc) : "memory");
 }
 
-// 3-D tiled load global -> shared, completion counted in bytes on an mbarrier of this CTA.
-__device__ __forceinline__ void tma_load_3d(uint32_t smemDst, const void* desc, uint32_t bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smemDst), "l"(desc), "r"(bar), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-
 // 4-D tiled load global -> shared (head dim, head, row within the batch entry, batch entry).
 __device__ __forceinline__ void tma_load_4d(uint32_t smemDst, const void* desc, uint32_t bar, int x, int y, int z, int w) {
   asm volatile(
@@ -104,10 +106,20 @@ __device__ __forceinline__ void tma_prefetch_4d(const void* desc, int x, int y, 
                : "memory");
 }
 
-// Same box pulled into L2 only (no shared-memory destination, no completion to wait for).
-__device__ __forceinline__ void tma_prefetch_3d(const void* desc, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(desc), "r"(x), "r"(y), "r"(z)
+// Tensor maps that are completed on the device (the host cannot know a dimension without reading it back):
+// the map is edited in shared memory, published to global memory with a release that orders the generic-proxy
+// writes before later tensor-map-proxy reads, and acquired by the thread that will issue TMA copies through it.
+__device__ __forceinline__ void tensormap_set_dim2(uint32_t smemMap, uint32_t extent) {
+  asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 2, %1;" ::"r"(smemMap), "r"(extent) : "memory");
+}
+// warp-collective: copies the 128-byte map from shared to global memory
+__device__ __forceinline__ void tensormap_publish(void* globalMap, uint32_t smemMap) {
+  asm volatile("tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;" ::"l"(globalMap),
+               "r"(smemMap)
                : "memory");
+}
+__device__ __forceinline__ void tensormap_acquire(const void* globalMap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(globalMap) : "memory");
 }
 
 // ---------------------------------------------------------------- register reallocation
@@ -156,33 +168,8 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]; 16-bit inputs, fp32 accumulate.  One thread issues.
-__device__ __forceinline__ void mma_ss(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(dTmem),
-      "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate)
-      : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem desc].
-__device__ __forceinline__ void mma_ts(uint32_t dTmem, uint32_t aTmem, uint64_t bDesc, uint32_t iDesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}\n" ::"r"(dTmem),
-      "r"(aTmem), "l"(bDesc), "r"(iDesc), "r"(accumulate)
-      : "memory");
-}
-
-// Same two instructions with the 64-bit shared-memory descriptors passed as (lo, hi) words, so that stepping a
+// D[tmem] (+)= A * B, 16-bit inputs, fp32 accumulate, one thread issues; A from shared memory (mma_ss_lohi) or from
+// tensor memory (mma_ts_lohi).  The 64-bit shared-memory descriptors are passed as (lo, hi) words, so that stepping a
 // descriptor through a tile is a single 32-bit add on the lo word (start address field, 16-byte units).
 __device__ __forceinline__ void mma_ss_lohi(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
                                             uint32_t iDesc, uint32_t accumulate) {
@@ -235,18 +222,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -264,10 +239,6 @@ __host__ __device__ __forceinline__ constexpr uint64_t smem_desc_sw128(uint32_t 
          (static_cast<uint64_t>((sboBytes >> 4) & 0x3FFF) << 32) | (static_cast<uint64_t>(1) << 46) |
          (static_cast<uint64_t>(2) << 61);
 }
-__device__ __forceinline__ uint64_t smem_desc_at(uint64_t templ, uint32_t smemAddr) {
-  return templ | static_cast<uint64_t>((smemAddr >> 4) & 0x3FFF);
-}
-
 // Instruction descriptor for kind::f16, fp32 accumulate.  fmt: 0 = fp16, 1 = bf16.
 __host__ __device__ __forceinline__ constexpr uint32_t instr_desc_f16(int fmt, int M, int N, int aMajorMN,
                                                                       int bMajorMN) {

@@ -47,12 +47,8 @@ struct FwdProblem {
   cudaStream_t stream;
 };
 
-// Word written by kernels when a bounded wait gives up: (launch epoch << 8) | site code.
-struct DeviceStatusWord {
-  int word;
-};
+// The device status word holds 0, or (launch epoch << 8) | site code once a bounded wait inside a kernel gave up.
 
-int launch_fwd_tc(const FwdProblem& p);      // fp16 / bf16: tcgen05 + TMEM + TMA kernel family
 int launch_fwd_fp32(const FwdProblem& p);    // fp32: CUDA-core FMA kernel
 void set_error_string(const char* fmt, ...);
 // argument checks shared by every entry point (c_abi.cu); both return a Status
