@@ -29,6 +29,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "ptx_sm100.cuh"
 #include "tfa_common.cuh"
 
@@ -78,7 +80,12 @@ constexpr int kRegsIssue = 64;
 constexpr int kRegsAtLaunch = (65536 / kThreads) / 8 * 8;
 static_assert(8 * kRegsSoftmax + 4 * kRegsEpilogue + 4 * kRegsIssue <= (kThreads / 32) * kRegsAtLaunch,
               "register budget: the CTA's launch allocation must cover every role's setmaxnreg value");
-constexpr float kRescaleLog2 = 8.0f;  // lazy-rescale threshold, log2 units
+// Lazy-rescale threshold, log2 units.  Price in accuracy, measured on the benchmark shapes against fp64: the mean
+// output error is 3-4 % above that of exact running maxima (and of the reference kernels), the maximum error within one
+// unit in the last place of the output type.  With the exact maximum the largest weights of a row sit just below 1.0,
+// at the top of a binade where the 16-bit P is most precise (the maximum itself is exactly 1.0); a stale reference
+// value spreads them over the binade.  Threshold 0 restores the last 3 % and makes most blocks take the rescale path.
+constexpr float kRescaleLog2 = 8.0f;
 constexpr int kSubTileBytes = 128 * 128;  // 128 rows x 128 bytes (64 16-bit elements), one swizzle-128B slab
 
 template <int HDP>
@@ -107,6 +114,29 @@ struct Cfg {
   static constexpr int kSmemBytes = (kNT * kQBufs + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
 };
 
+// Head dim <= 64, second form: ONE Q tile per CTA and TWO CTAs per SM (8 warps each: 4 softmax warps that also
+// write the output, one MMA-issuing and one loading thread, two idle warps).  The two tiles of an SM then belong to different work
+// items, so one CTA's item boundary (output, next item's first loads and scores) runs while the other CTA computes,
+// instead of both tiles of one CTA standing at the same boundary.  Tensor memory: 256 columns per CTA - S rotating in
+// 192 as above, O in the last 64.  Shared memory: two Q buffers and four K/V stages of 16 KB, 99 KB per CTA.
+struct CfgSolo64 {
+  static constexpr int kSub = 1;
+  static constexpr int kTileBytes = kSubTileBytes;
+  static constexpr int kNT = 1;
+  static constexpr int kQBufs = 2;
+  static constexpr int kStages = 4;
+  static constexpr int kTmemCols = 256;
+  static constexpr bool kRot = true;
+  static constexpr bool kDblS = false;
+  static constexpr bool kTwoPos = true;
+  static constexpr int kSPosStride = 64;
+  static constexpr int kPPosStride = 128;
+  static constexpr int kSRegion = 192;
+  static constexpr int kOCol0 = 192;
+  static constexpr int kSmemBytes = (kNT * kQBufs + kStages) * kTileBytes + 2048 + 1024;
+};
+constexpr int kThreadsSolo = 256;  // two whole warpgroups (setmaxnreg is a warpgroup-wide instruction); warps 6 and 7 idle
+
 // Barrier slots (8 bytes each) inside the control block that follows the tiles.
 // A parity wait can only tell "the phase in progress" from "the phase just completed": a waiter must never fall
 // two phases behind its barrier.  Where a producer may legitimately run two uses ahead (Q tiles with two buffers,
@@ -128,20 +158,6 @@ enum Bar : int {
   kBarKvEmpty = 38,    // [kStages <= 6]
   kNumBars = 48,
 };
-
-// Optional timeline instrumentation (debug builds only, -DTFA_TRACE): one CTA records clock64() at named points.
-#ifdef TFA_TRACE
-constexpr int kTraceRoles = 5, kTraceIters = 64, kTracePts = 8;
-__device__ unsigned long long g_trace[kTraceRoles * kTraceIters * kTracePts];
-#define TFA_TR(role, iter, pt)                                                                      \
-  do {                                                                                              \
-    if (traceOn && (iter) < kTraceIters) g_trace[((role) * kTraceIters + (iter)) * kTracePts + (pt)] = clock64(); \
-  } while (0)
-#else
-#define TFA_TR(role, iter, pt) \
-  do {                         \
-  } while (0)
-#endif
 
 constexpr int kWorkConsumers = 14;  // 8 softmax warps + 4 epilogue warps + 2 MMA-issuing threads
 
@@ -265,9 +281,12 @@ __device__ __forceinline__ float2 fadd2_rm(float2 a, float2 b) {  // round towar
 }
 
 // exp2 on the FMA pipe for a pair of values (the MUFU unit is the co-bottleneck of this kernel: 16 ex2/clk/SM
-// against 128x128 exponentials per tile-block).  x = floor(x) + f; 2^f by a cubic with p(0) = 1 (max relative
-// error 8.6e-5, below the rounding of the 16-bit P it feeds); 2^floor(x) by adding to the exponent field.
-// The magic constant 1.5*2^23 makes the low mantissa bits of t hold floor(x); x is clamped at -127.
+// against 128x128 exponentials per tile-block).  x = floor(x) + f; 2^f by a minimax polynomial with p(0) = 1;
+// 2^floor(x) by adding to the exponent field.  The magic constant 1.5*2^23 makes the low mantissa bits of t hold
+// floor(x); x is clamped at -127.  The result feeds the 16-bit P, so the polynomial only has to stay below that
+// type's rounding: a cubic for bf16 (max relative error 8.6e-5 against 2^-9), a quartic for fp16 (2.9e-6 against
+// 2^-12; with the cubic the mean output error was 3.5 % above the reference kernels' on the fp16 benchmark shape).
+template <bool kQuartic>
 __device__ __forceinline__ float2 ex2_fma2(float2 x) {
   const float kMagic = 12582912.f;
   x.x = fmaxf(x.x, -127.f);
@@ -275,8 +294,15 @@ __device__ __forceinline__ float2 ex2_fma2(float2 x) {
   const float2 t = fadd2_rm(x, make_float2(kMagic, kMagic));
   const float2 xi = fadd2(t, make_float2(-kMagic, -kMagic));
   const float2 f = ffma2(xi, make_float2(-1.f, -1.f), x);
-  float2 p = ffma2(make_float2(0.07706704f, 0.07706704f), f, make_float2(0.22764499f, 0.22764499f));
-  p = ffma2(p, f, make_float2(0.69511679f, 0.69511679f));
+  float2 p;
+  if constexpr (kQuartic) {
+    p = ffma2(make_float2(0.013425155f, 0.013425155f), f, make_float2(0.052245375f, 0.052245375f));
+    p = ffma2(p, f, make_float2(0.24127856f, 0.24127856f));
+    p = ffma2(p, f, make_float2(0.69304514f, 0.69304514f));
+  } else {
+    p = ffma2(make_float2(0.07706704f, 0.07706704f), f, make_float2(0.22764499f, 0.22764499f));
+    p = ffma2(p, f, make_float2(0.69511679f, 0.69511679f));
+  }
   p = ffma2(p, f, make_float2(1.f, 1.f));
   p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
   p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
@@ -403,12 +429,18 @@ __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
 // fixed-length speed; the masking code 8 % at head dim 64 and nothing at 128 / 256, so mode 2 is only built for
 // the 64 kernel).
 constexpr int kModeFixed = 0, kModeVarlen = 1, kModeFixedNoMask = 2;
-template <int HDP, bool kBf16, int kMode>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int HDP, bool kBf16, int kMode, bool kSolo = false>
+__global__ void __launch_bounds__(kSolo ? kThreadsSolo : kThreads, kSolo ? 2 : 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
-  using C = Cfg<HDP>;
+  static_assert(!kSolo || HDP == 64, "the one-tile, two-CTAs-per-SM form exists for padded head dim 64 only");
+  using C = typename std::conditional<kSolo, CfgSolo64, Cfg<HDP>>::type;
   constexpr int NT = C::kNT;
+  // warp roles: softmax warps [0, 4 * NT'), epilogue warps, the two MMA-issuing warps, the loading warp
+  constexpr int kSoftmaxWarps = kSolo ? 4 : 8;
+  constexpr int kEpilogueEnd = kSolo ? 4 : 12;  // epilogue warps are [kSoftmaxWarps, kEpilogueEnd): none in the solo form
+  constexpr int kIssueWarpA = kSolo ? 4 : 12, kIssueWarpB = kSolo ? -1 : kIssuerB, kLoadWarp = kSolo ? 5 : 13;
+  constexpr int kConsumers = kSolo ? 5 : kWorkConsumers;  // roles that read every work item
   constexpr int NS = C::kStages;
   constexpr bool kVarlen = (kMode == kModeVarlen);
   static_assert(NS <= 6, "barrier slots");
@@ -441,7 +473,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::mbar_init(bar(kBarScaleFull + t), 4);
       ptx::mbar_init(bar(kBarOFree + t), 4);
       ptx::mbar_init(bar(kBarWorkFull + t), 1);
-      ptx::mbar_init(bar(kBarWorkEmpty + t), kWorkConsumers);
+      ptx::mbar_init(bar(kBarWorkEmpty + t), kConsumers);
     }
     for (int s = 0; s < NS; s++) {
       ptx::mbar_init(bar(kBarKvFull + s), 1);
@@ -451,7 +483,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
   }
-  if (warp == 12) {
+  if (warp == kIssueWarpA) {
     ptx::tmem_alloc(ptx::smem_u32(&ctl->tmemBase), C::kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -466,7 +498,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       mapV = p.devMaps + 2;
     }
   }
-  if (warp == 13 && lane == 0) {
+  if (warp == kLoadWarp && lane == 0) {
     if (kVarlen && p.devMaps != nullptr) {
       ptx::tensormap_acquire(mapQ);
       ptx::tensormap_acquire(mapK);
@@ -482,13 +514,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmemBase;
   const WaitCtx wc{&ctl->failed, p.status, p.epoch};
-#ifdef TFA_TRACE
-  const bool traceOn = (blockIdx.x == gridDim.x / 2) && lane == 0;
-  if (traceOn && warp == 14) {  // SM clock against wall clock over the life of this CTA
-    g_trace[(2 * kTraceIters + 0) * kTracePts + 0] = clock64();
-    g_trace[(2 * kTraceIters + 0) * kTracePts + 1] = ptx::global_timer_ns();
-  }
-#endif
 
   // Every consumer of work items (8 softmax warps, 4 epilogue warps, 2 MMA threads) reads item k from slot k & 1
   // and frees the slot; a negative index ends the loop.
@@ -509,7 +534,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     return ws->idx;
   };
 
-  if (warp < 8) {
+  if (warp < kSoftmaxWarps) {
     // ================================================================ softmax
     ptx::setmaxnreg_inc<kRegsSoftmax>();
     const int t = warp >> 2;
@@ -536,7 +561,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int j = 0; j < n; j++, it++) {
         wait_bar(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)), (C::kTwoPos ? (it >> 1) : it) & 1, wc, 1);
         ptx::tc_fence_after();
-        if ((warp & 3) == 0) TFA_TR(t, it, 0);
         uint32_t v[4][32];
         const uint32_t tS = tRegion + (uint32_t)((it & 1) * C::kSPosStride);   // S of this block
         const uint32_t tP = tRegion + (uint32_t)((it & 1) * C::kPPosStride);   // where its P goes
@@ -551,7 +575,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar(kBarSFree + t));
         }
-        if ((warp & 3) == 0) TFA_TR(t, it, 1);
 
         const int kbase = j * kBlockN;
         const bool needMask = (kMode != kModeFixedNoMask) &&
@@ -576,7 +599,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             float2 x = make_float2(__uint_as_float(vq[i]), __uint_as_float(vq[i + 1]));
             x = ffma2(x, c2, negMc2);
             if (((i >> 1) % kEmuPeriod) < kEmuCount) {  // compile-time pattern: this pair goes to the FMA pipe
-              x = ex2_fma2(x);
+              x = ex2_fma2<!kBf16>(x);
             } else {
               x.x = ex2(x.x);
               x.y = ex2(x.y);
@@ -596,7 +619,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           for (int i = 2; i < 32; i += 2) mx4[q] = fmax3(mx4[q], __uint_as_float(v[q][i]), __uint_as_float(v[q][i + 1]));
         }
         const float mx = fmax2(fmax2(mx4[0], mx4[1]), fmax2(mx4[2], mx4[3]));  // NaN if any score of the row is
-        if ((warp & 3) == 0) TFA_TR(t, it, 2);
         // Lazy rescale: keep the old reference max while the new one exceeds it by less than kRescaleLog2 in
         // the exp2 domain (P then grows up to 2^kRescaleLog2, harmless in fp32 sums and 16-bit P); the
         // result is unchanged because O and the row sum stay relative to the same reference value.
@@ -629,7 +651,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (m != -INFINITY && !grow) mNew = m;
         const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
         m = mNew;
-        if ((warp & 3) == 0) TFA_TR(t, it, 3);
 
         // A NaN score makes every exponential of the row NaN (the pairs evaluated on the FMA pipe clamp their
         // argument and would turn a NaN of their own into 0), hence the row sum and the output row.
@@ -644,7 +665,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             expQuarter(v[2], negMc, pkA, sum2);
             expQuarter(v[3], negMc, pkB, sum2);
           }
-          if ((warp & 3) == 0) TFA_TR(t, it, 4 + 2 * half);
           if constexpr (kVarlen) {
            if (half == 0 && kbase + kBlockN > w.skv) {
             // Packed variable-length input: the rows of this V block past the end of the sequence are the next
@@ -664,9 +684,47 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + 2 * t + pSlot));
-          if ((warp & 3) == 0) TFA_TR(t, it, 5 + 2 * half);
         }
         l += sum2.x + sum2.y;
+      }
+      if constexpr (kSolo) {
+        // This warp is also the epilogue of its 32 rows: wait for the last P.V of the item, read O, release the
+        // accumulator to the next item, normalise, convert and store.  Meanwhile the SM's other CTA keeps computing.
+        const int lastBlk = it - 1;
+        wait_bar(bar(kBarPvDone + 2 * t + (lastBlk & 1)), (lastBlk >> 1) & 1, wc, 7);
+        ptx::tc_fence_after();
+        const float inv = (l > 0.f) ? (1.f / l) : 0.f;
+        const int gp = 1 << p.packShift;
+        const int head = (w.unit << p.packShift) + (r & (gp - 1));
+        const bool valid = qpos < w.sq;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.O) +
+                                              ((w.qRow0 + qpos) * p.headsQ + head) * (long long)p.headDim);
+        const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
+#pragma unroll
+        for (int ch = 0; ch < HDP / 32; ch++) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
+          ptx::tmem_wait_ld();
+          ptx::tmem_ld_fence(o);
+          if (ch == HDP / 32 - 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kBarOFree + t));
+          }
+          if (valid && ch * 32 < p.headDim) {
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+              uint4 q;
+              q.x = pack2<kBf16>(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+              q.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+              q.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+              q.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+              dst[ch * 4 + g] = q;
+            }
+          }
+        }
+        items++;
+        continue;
       }
       // final row sums for the epilogue; the slot is free once the epilogue of the previous item has released O
       if (items > 0) wait_bar(bar(kBarOFree + t), (items - 1) & 1, wc, 3);
@@ -675,7 +733,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (lane == 0) ptx::mbar_arrive(bar(kBarScaleFull + t));
       items++;
     }
-  } else if (warp < 12) {
+  } else if (warp < kEpilogueEnd) {
     // ================================================================ epilogue
     ptx::setmaxnreg_dec<kRegsEpilogue>();
     const int r = threadIdx.x & 127;
@@ -738,7 +796,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
   } else {
     ptx::setmaxnreg_dec<kRegsIssue>();
-    if ((warp == 12 || warp == kIssuerB) && lane == 0) {
+    if ((warp == kIssueWarpA || warp == kIssueWarpB) && lane == 0) {
       // ============================================================== MMA issue
       const int fmt = kBf16 ? 1 : 0;
       const uint32_t idQK = ptx::instr_desc_f16(fmt, kBlockM, kBlockN, 0, 0);
@@ -751,7 +809,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const uint32_t kLoT = (uint32_t)descK, vLoT = (uint32_t)descV;  // LBO field; start address added below
       // Issue helpers.  The tensor pipe overlaps at most one MMA with the issuing thread's next instructions, so
       // everything between two tcgen05.mma costs tensor time: per MMA there is one 32-bit add on a descriptor word.
-      const int t = (warp != 12) ? 1 : 0;
+      const int t = (warp != kIssueWarpA) ? 1 : 0;
       const uint32_t qLo0 = kLoT | ((sQ + (uint32_t)t * C::kQBufs * C::kTileBytes) >> 4);
       uint32_t qLo = qLo0;  // Q buffer of the current item
       const uint32_t dRegion = tmem + (uint32_t)(t * C::kSRegion);
@@ -800,7 +858,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         Work w;
         const int idx = fetchWork(k, w);
         ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
-        TFA_TR(2, k, t * 4 + 1);
         if (idx < 0 || *wc.failed) break;
         if (w.nmax == 0) continue;
         const int n = (t < NT) ? w.nblk[t] : 0;
@@ -830,7 +887,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         {
           const int s0 = ld % NS;
           const uint32_t ph0 = (ld / NS) & 1;
-          TFA_TR(2, k, t * 4 + 2);
           if (n > 0) {
             wait_bar(bar(kBarKvFull + s0), ph0, wc, 8);
             wait_bar(bar(kBarQFull + 2 * t + (qc % C::kQBufs)), (qc / C::kQBufs) & 1, wc, 9);
@@ -840,7 +896,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (n > 0) {
             issueQK(it, sKV + s0 * C::kTileBytes, 0);
             issueQK(it, sKV + s0 * C::kTileBytes, 1);
-            TFA_TR(2, k, t * 4 + 3);
             ptx::tc_commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
             if (n == 1) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
           }
@@ -882,20 +937,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
               ptx::tc_commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
               if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
-              TFA_TR(3, blk, t * 4 + 3);
             }
             if (j < n) {
               wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
               if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
               wait_bar(bar(kBarP0Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 11);
               ptx::tc_fence_after();
-              TFA_TR(3, blk, t * 4 + 0);
               issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
               wait_bar(bar(kBarP1Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 15);
               ptx::tc_fence_after();
-              TFA_TR(3, blk, t * 4 + 1);
               issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
-              TFA_TR(3, blk, t * 4 + 2);
               ptx::tc_commit(bar(kBarPvDone + 2 * t + (blk & 1)));
             }
             if (hasNext) release(sK, j + 1 < n);
@@ -916,49 +967,39 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           // the tensor pipe idle.  MMAs of the two tiles touch disjoint tensor memory, so interleaving is harmless.
           if (j < n) {
             ptx::tc_fence_after();
-            TFA_TR(3, blk, t * 4 + 0);
             issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
             if (!p1Ready) {
               spin_bar(bar(kBarP1Ready + 2 * t), blk & 1, wc, 15);
               ptx::tc_fence_after();
             }
-            TFA_TR(3, blk, t * 4 + 1);
             issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
-            TFA_TR(3, blk, t * 4 + 2);
             if (j + 1 < n) {
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
               passTurn();
               issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
               ptx::tc_commit(bar(kBarSFull + 2 * t));
               if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
-              TFA_TR(3, blk, t * 4 + 3);
             } else {
               passTurn();
             }
             ptx::tc_commit(bar(kBarPvDone + 2 * t));
-            TFA_TR(2, blk, t * 4 + 0);
           } else {
             passTurn();
           }
           release(sV, j < n);
-          TFA_TR(2, blk, t * 4 + 1);
           if (hasNext) {
             release(sK, j + 1 < n);
             ld++;
           }
-          TFA_TR(2, blk, t * 4 + 2);
         }
         it += n;
         if (n > 0) qc++;
-        TFA_TR(2, k + 1, t * 4 + 0);
       }
-    } else if (warp == 13 && lane == 0) {
+    } else if (warp == kLoadWarp && lane == 0) {
       // ============================================================== work distribution + TMA loads
       const int gp = 1 << p.packShift;
       int ld = 0;            // KV-ring loads issued so far
       int qc[2] = {0, 0};    // Q loads issued so far per tile
-      bool pendQ[2] = {false, false};  // a Q load of tile t is noted but not issued yet (its buffer is still in use)
-      int pq[2][3];                    // ... and its coordinates: head, row, batch entry
       // Takes the next work index, works out its description and publishes both in slot k & 1 (free once every
       // consumer has read item k - 2 from it).  Returns false when the work has run out.
       Work wq[2];
@@ -984,7 +1025,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ws->nblk[1] = w.nblk[1];
         ws->nmax = w.nmax;
         ptx::mbar_arrive(bar(kBarWorkFull + (k & 1)));  // release: the stores above are visible to whoever waits
-        TFA_TR(4, k, 4);
         return idx >= 0;
       };
       bool more = publish(0);
@@ -1002,85 +1042,33 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) ptx::tma_prefetch_4d(mapQ, a * 64, w.unit * gp, w.qRowTma + w.qlo[t], w.batchTma);
         }
-        // Q loads never hold up the K/V stream.  A Q buffer is free only once the tile's last Q.K^T of the previous
-        // item has finished, which for tile 1 is a block later than for tile 0; a loader that waited for it in program
-        // order would keep the next item's first K/V blocks out of ring stages that are free already, and the tiles
-        // would start the item with nothing prefetched.  So a Q load is only noted here (pendQ) and issued from
-        // wherever this thread next polls, as soon as its buffer is free.
-        auto tryQ = [&](int t) -> bool {  // true: nothing pending for tile t (any more)
-          if (t >= NT || !pendQ[t]) return true;
+        auto loadQ = [&](int t) {
+          if (t >= NT || w.nblk[t] == 0) return;
+          // buffer qc % kQBufs was last used by item qc - kQBufs of this tile
           const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;  // buffer and how often it was used before
-          if (qUse > 0 && !ptx::mbar_test_wait(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1)) return false;
+          if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
           ptx::mbar_arrive_expect_tx(bar(kBarQFull + 2 * t + qb), C::kTileBytes);
           const uint32_t qDst = sQ + (t * C::kQBufs + qb) * C::kTileBytes;
 #pragma unroll
           for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_4d(qDst + a * kSubTileBytes, mapQ, bar(kBarQFull + 2 * t + qb), a * 64, pq[t][0], pq[t][1], pq[t][2]);
+            ptx::tma_load_4d(qDst + a * kSubTileBytes, mapQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
+                             w.qRowTma + w.qlo[t], w.batchTma);
           }
           qc[t]++;
-          pendQ[t] = false;
-          TFA_TR(4, k, 5 + t);
-          return true;
         };
-        // Wait for a barrier phase while a Q load is pending: suspended waits of at most 200 ns (no spinning: the
-        // warps that share this thread's scheduler need the issue slots), a look at the Q buffers in between.  With
-        // nothing pending it is the plain bounded wait.
-        auto waitWatchingQ = [&](uint32_t barAddr, uint32_t parity, int site) {
-          uint32_t rounds = 0;
-          uint64_t t0 = 0;
-          while (pendQ[0] || pendQ[1]) {
-            if (ptx::mbar_try_wait_ns(barAddr, parity, 200)) return;
-            tryQ(0);
-            tryQ(1);
-            if ((++rounds & 0x3F) == 0) {
-              if (*wc.failed) return;
-              const uint64_t now = ptx::global_timer_ns();
-              if (t0 == 0) {
-                t0 = now;
-              } else if (now - t0 > 2000000000ull) {
-                *wc.failed = 1;
-                atomicExch(wc.status, (wc.epoch << 8) | site);
-                return;
-              }
-            }
-          }
-          wait_bar(barAddr, parity, wc, site);
-        };
-        auto noteQ = [&](int t) {
-          if (t >= NT || w.nblk[t] == 0) return;
-          if (pendQ[t]) {  // the tile's previous Q load has to go out first (two items behind: rare)
-            const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;
-            if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
-            tryQ(t);
-          }
-          pq[t][0] = w.unit * gp;
-          pq[t][1] = w.qRowTma + w.qlo[t];
-          pq[t][2] = w.batchTma;
-          pendQ[t] = true;
-          tryQ(t);
-#ifdef TFA_X_NOPOLL
-          if (pendQ[t]) {
-            const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;
-            if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
-            tryQ(t);
-          }
-#endif
-        };
-        // Order when nothing has to wait: Q of tile 0, the first K block, Q of tile 1, everything else.  Tile 0 finishes
-        // an item first (causal: one block earlier), so its Q buffer is free while tile 1 still computes; its first
-        // Q.K^T of this item then needs only these two loads and overlaps the end of the previous item.
-        noteQ(0);
+        // Order: Q of tile 0, the first K block, Q of tile 1, everything else.  Tile 0 finishes an item first (causal:
+        // one block earlier), so its Q buffer is free while tile 1 still computes; its first Q.K^T of this item then
+        // needs only these two loads and overlaps the end of the previous item.
+        loadQ(0);
         const int numLoads = 2 * w.nmax;
         for (int i = 0; i < numLoads; i++, ld++) {
-          if (i == 1) noteQ(1);
+          if (i == 1) loadQ(1);
           if (i == numLoads - 4 && !nextDone) {
             more = publish(k + 1);
             nextDone = true;
           }
           const int s = ld % NS;
-          if (ld >= NS) waitWatchingQ(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, 14);
-          TFA_TR(4, i >> 1, (i & 1) * 2);
-          if (i == 0) TFA_TR(4, k, 7);
+          if (ld >= NS) wait_bar(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, wc, 14);
           ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
           bool isV;
           int blkIdx;
@@ -1113,27 +1101,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
         if (!nextDone) more = publish(k + 1);
-        if (!more) {  // last item: nothing may stay behind
-#pragma unroll
-          for (int t = 0; t < NT; t++) {
-            if (!pendQ[t]) continue;
-            const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;
-            if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 23);
-            tryQ(t);
-          }
-        }
       }
     }
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-#ifdef TFA_TRACE
-  if (traceOn && warp == 14) {
-    g_trace[(2 * kTraceIters + 0) * kTracePts + 2] = clock64();
-    g_trace[(2 * kTraceIters + 0) * kTracePts + 3] = ptx::global_timer_ns();
-  }
-#endif
   if (threadIdx.x == 0) {
     // The last CTA to get here puts both counters back to zero for the next launch that uses them.  Every CTA's
     // fetches from the work counter precede its arrival on the done counter (same CTA, separated by the barrier above).
@@ -1149,7 +1122,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       p.workCounter[1] = 0;
     }
   }
-  if (warp == 12) {
+  if (warp == kIssueWarpA) {
     if (*wc.failed) __nanosleep(200000);  // a wait gave up: let whatever is still in flight drain before freeing
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, C::kTmemCols);

@@ -31,6 +31,7 @@ int* device_work_counter(int device, cudaStream_t stream, int* rc, CUtensorMap**
 int launch_patch_varlen_maps(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, CUtensorMap* out,
                              const int* cuQ, const int* cuKV, int batch, cudaStream_t stream);  // c_abi.cu
 int device_num_sms(int device);       // c_abi.cu
+int option_solo64();                  // c_abi.cu: one-tile CTAs, two per SM, for head dims 32 / 64
 int option_work_order();              // c_abi.cu: -1 auto, 0 pair index fastest, n > 0 chunk width
 
 #define TFA_CAT3(a, b, c) a##b##c
@@ -64,10 +65,20 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   const bool varlen = (pr.cuQ != nullptr);
   auto kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen>
                        : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed>;
+  bool solo = false;  // one Q tile per CTA, two CTAs per SM (padded head dim 64 only)
+  int kNT = C::kNT, smemBytes = C::kSmemBytes, threads = tc::kThreads;
 #if TFA_HDP == 64
   // nothing to mask: not causal, and the key length fills its last 128-key block
-  if (!varlen && !pr.causal && pr.seqLenKV % tc::kBlockN == 0) {
-    kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>;
+  const bool noMask = !varlen && !pr.causal && pr.seqLenKV % tc::kBlockN == 0;
+  if (noMask) kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>;
+  solo = option_solo64() != 0;
+  if (solo) {
+    kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen, true>
+                    : (noMask ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask, true>
+                              : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed, true>);
+    kNT = 1;
+    smemBytes = tc::CfgSolo64::kSmemBytes;
+    threads = tc::kThreadsSolo;
   }
 #endif
 
@@ -88,6 +99,17 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
       attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     }
+    // the two-CTAs-per-SM form: 99 KB each, and the largest shared-memory carve-out so that two fit
+    auto soloAttr = [&](auto k) {
+      if (attrErr[device] != cudaSuccess) return;
+      attrErr[device] = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::CfgSolo64::kSmemBytes);
+      if (attrErr[device] == cudaSuccess) {
+        attrErr[device] = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      }
+    };
+    soloAttr(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed, true>);
+    soloAttr(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen, true>);
+    soloAttr(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask, true>);
 #endif
   });
   if (attrErr[device] != cudaSuccess) {
@@ -119,7 +141,7 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   p.headDim = pr.headDim;
   p.group = pr.headsQ / pr.headsKV;
   p.packShift = packShift;
-  const int seqPerCta = C::kNT * rowsPerTile;
+  const int seqPerCta = kNT * rowsPerTile;
   p.numPairs = (pr.seqLenQ + seqPerCta - 1) / seqPerCta;
   p.causal = pr.causal;
   p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)pr.headDim));
@@ -165,9 +187,10 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
     p.devMaps = slotMaps;
   }
 
-  // persistent: one CTA per SM (512 tensor-memory columns and ~200 KB of shared memory each)
-  const int ctas = (int)(numWork < device_num_sms(device) ? numWork : device_num_sms(device));
-  kernel<<<dim3((unsigned)ctas), tc::kThreads, C::kSmemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
+  // persistent: one CTA per SM (512 tensor-memory columns and ~200 KB of shared memory each), or two of the small form
+  const long long slots = (long long)device_num_sms(device) * (solo ? 2 : 1);
+  const int ctas = (int)(numWork < slots ? numWork : slots);
+  kernel<<<dim3((unsigned)ctas), threads, smemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error_string("kernel launch failed: %s", cudaGetErrorString(e));
@@ -176,15 +199,5 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   return kOk;
 }
 
-#ifdef TFA_TRACE
-// debug builds only: copy the timeline of the instrumented CTA to the host
-extern "C" int tfa_b200_debug_read_trace(unsigned long long* host, int count) {
-  const int n = tc::kTraceRoles * tc::kTraceIters * tc::kTracePts;
-  if (count < n) return -1;
-  cudaDeviceSynchronize();
-  if (cudaMemcpyFromSymbol(host, tc::g_trace, sizeof(unsigned long long) * n) != cudaSuccess) return -2;
-  return n;
-}
-#endif
 
 }  // namespace tfa_b200
