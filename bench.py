@@ -20,7 +20,7 @@ Prints ONE JSON line.  `value` is throughput with inputs resident in HBM, over t
 the same metric through the public Python API with pinned HOST buffers (host->device copies of Q, K, V and
 device->host copy of O inside the timed region; median of per-step times).  `roofline` holds the kernel alone
 through the C ABI (median of per-launch CUDA-event times) against the measured burst peak, and in
-`roofline.sustained` a 400-launch back-to-back loop against the measured sustained peak with the SM clock sampled
+`roofline.sustained` a back-to-back loop of at least 400 launches and 0.6 s against the measured sustained peak with the SM clock sampled
 during that loop.  `--impl reference` runs the reference's own CUDA kernels (built for sm_100a from the
 reference sources by oracle/Makefile) through the reference's tfa::flashAttn API on the same shape; if that
 library was not built it times the reference's CPU attention instead and says so.
@@ -52,6 +52,14 @@ WORKLOADS = {
     # 16 packed sequences, lengths uniform in [128, 8192] from the seed, same length for Q and K/V
     "bf16_causal_varlen_gqa_16seq_h32_8_d128": {"kind": "varlen", "dtype": "bf16", "causal": True, "nseq": 16,
                                                 "lo": 128, "hi": 8192, "seed": 0, "Hq": 32, "Hkv": 8, "D": 128},
+    # one long sequence and fifteen short ones: a grid sized by the longest sequence is almost all dead tiles
+    # (the reference launches them, reference csrc/flash_attn/launcher.cuh:98)
+    "bf16_causal_varlen_gqa_1long_15short_h32_8_d128": {"kind": "varlen", "dtype": "bf16", "causal": True,
+                                                        "lens": [8192] + [128] * 15, "Hq": 32, "Hkv": 8, "D": 128},
+    # small shapes of the reference's own test and benchmark lists (reference tests/cpp/test_flash_attn.cu:388-420,
+    # benchmarks/benchmark.py:23): launch- and latency-bound
+    "bf16_causal_b2_s512_h32_d128": _fixed("bf16", True, 2, 512, 512, 32, 32, 128),
+    "fp16_noncausal_b2_s128_h4_d64": _fixed("fp16", False, 2, 128, 128, 4, 4, 64),
     "fp16_causal_b8_s2048_h16_d32": _fixed("fp16", True, 8, 2048, 2048, 16, 16, 32),
     "fp16_causal_b8_s2048_h16_d64": _fixed("fp16", True, 8, 2048, 2048, 16, 16, 64),
     "fp16_causal_b8_s2048_h16_d96": _fixed("fp16", True, 8, 2048, 2048, 16, 16, 96),
@@ -68,11 +76,20 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "bf16_noncausal_b2_s4096_h32_d128"
 STRONG_WORKLOADS = ("bf16_causal_gqa_b4_s8192_h32_8_d128", "bf16_causal_varlen_gqa_16seq_h32_8_d128")
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-# (decode: batch-8 capture scaled by units processed; traffic grows in proportion to batch).
+# (decode batch 64: the batch-8 capture scaled by units processed; traffic grows in proportion to batch).
 NCU_TRAFFIC_BYTES = {
-    "bf16_noncausal_b2_s4096_h32_d128": 201475328 + 46450432,
-    "bf16_decode_b64_skv32768_h32_8_d128": int((1074021000 + 4879104) * 8),
-    "bf16_decode_b8_skv32768_h32_8_d128": 1074021000 + 4879104,
+    "bf16_noncausal_b2_s4096_h32_d128": 246329088,
+    "bf16_causal_b2_s4096_h32_d128": 263884544,
+    "bf16_causal_varlen_gqa_16seq_h32_8_d128": 1348863488,
+    "bf16_causal_gqa_b4_s8192_h32_8_d128": 643794688,
+    "fp16_causal_b8_s2048_h16_d64": 115061248,
+    "fp16_causal_b8_s2048_h16_d32": 52957696,
+    "fp16_causal_b8_s2048_h16_d96": 183778048,
+    "fp16_causal_b8_s2048_h16_d192": 384580864,
+    "fp16_causal_b8_s2048_h16_d256": 523113216,
+    "fp32_noncausal_b2_s4096_h32_d128": 518427392,
+    "bf16_decode_b8_skv32768_h32_8_d128": 1078060032,
+    "bf16_decode_b64_skv32768_h32_8_d128": 8624480256,
 }
 FALLBACK_PEAK_TFLOPS = 1590.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 ESIZE = {"bf16": 2, "fp16": 2, "fp32": 4}
@@ -81,6 +98,8 @@ ESIZE = {"bf16": 2, "fp16": 2, "fp32": 4}
 def varlen_lengths(w):
     import numpy as np
 
+    if "lens" in w:
+        return list(w["lens"])
     rng = np.random.default_rng(w["seed"])
     return [int(x) for x in rng.integers(w["lo"], w["hi"] + 1, w["nseq"])]
 
@@ -484,7 +503,10 @@ def main():
     sustained = None
     if not args.no_sustained:
         # a longer back-to-back burst of the same kernel: throughput once the power cap has pulled the clock down
+        # at least 400 launches (100 for kernels of several ms) and at least ~0.6 s, so that the 50 ms clock sampler
+        # sees the loop
         n_sus = 400 if ms_kernel < 5 else 100
+        n_sus = min(20000, max(n_sus, int(600.0 / max(ms_kernel, 1e-3))))
         bracket(prob.step_kernel, 20, 0)
         t_sus0 = time.perf_counter()
         ms_sus = bracket(prob.step_kernel, n_sus, 0) / n_sus

@@ -672,6 +672,46 @@ def test_cuda_graph_capture_and_replay():
     tf.device_status()
 
 
+def test_many_streams_and_a_graph_replay_next_to_eager_launches():
+    """Work counters belong to a stream (eager launches) or to one captured launch (graphs), never to two launches
+    that can run at the same time: 100 streams with launches in flight, and a captured launch replayed on another
+    stream in between, all give the bits of a launch that ran alone, and no launch reports shared counters."""
+    lib = _lib.load()
+    dims = (1, 512, 512, 8, 8, 128)
+    B, Sq, Skv, Hq, Hkv, D = dims
+    Q, K, V = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in _fixed_inputs(dims, seed=17))
+    alone = torch.zeros_like(Q)
+    assert lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), alone.data_ptr(), 2, B, Sq, Skv, Hq, Hkv, D, 1,
+                            torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    Og = torch.zeros_like(Q)
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            rc = lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), Og.data_ptr(), 2, B, Sq, Skv, Hq, Hkv, D, 1,
+                                  torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.last_error()
+    streams = [torch.cuda.Stream() for _ in range(100)]
+    outs = [torch.zeros_like(Q) for _ in range(300)]
+    torch.cuda.synchronize()
+    replay_stream = torch.cuda.Stream()
+    for rep in range(3):
+        for i, st in enumerate(streams):
+            O = outs[rep * 100 + i]
+            assert lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), 2, B, Sq, Skv, Hq, Hkv, D, 1,
+                                    st.cuda_stream) == 0, _lib.last_error()
+            if i % 25 == 0:
+                with torch.cuda.stream(replay_stream):
+                    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(Og, alone)
+    for O in outs:
+        assert torch.equal(O, alone)
+    tf.device_status()
+
+
 @pytest.mark.parametrize("pack", [0, 1])
 def test_gqa_packing_modes_agree(pack):
     """Interleaving a KV group's Q heads into one tile is a scheduling choice, not a numerical one."""
