@@ -5,7 +5,7 @@
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
 ROOT="$(cd "$HERE/../.." && pwd)"
-REF="${REF:-/root/reference}"
+REF="${REF:-$(cd "$ROOT/.." && pwd)/reference}"  # default: a directory named reference beside this repository
 OUT="$HERE/_build"
 mkdir -p "$OUT"
 FLAGS="-std=c++17 -O2 -gencode arch=compute_100a,code=sm_100a -I$ROOT/include -I$HERE -I$REF/tests/cpp"

@@ -437,6 +437,11 @@ def test_varlen_without_totals_is_asynchronous_and_correct(hd):
     # the packed tensors end exactly at the totals: a tensor map with a larger extent would read past the allocation
     O1, O2 = torch.full_like(Qd, 5.0), torch.full_like(Qd, 5.0)
     stream = torch.cuda.Stream()
+    # one call beforehand: the first use of a kernel in a process loads its code and creates the per-device state,
+    # which synchronises the device and is not what this test is about
+    rc = lib.tfa_b200_fwd_varlen(Qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), O2.data_ptr(), cq.data_ptr(), ck.data_ptr(),
+                                 2, len(sq), max(sq), max(skv), -1, -1, Hq, Hkv, hd, 1, stream.cuda_stream)
+    assert rc == 0, _lib.last_error()
     torch.cuda.synchronize()
     with torch.cuda.stream(stream):
         torch.cuda._sleep(400_000_000)  # a bounded spin of roughly 0.2 s ahead of the call
