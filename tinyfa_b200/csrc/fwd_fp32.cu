@@ -328,6 +328,259 @@ __global__ void __launch_bounds__(BR * 8 / kRowsPerThread) fwd_fp32_kernel(const
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Second form of the fp32 kernel: "warp owns rows, lane owns columns"; used for head dim 256.
+//
+// A warp owns 8 query rows and a lane owns every 32nd key of a block: the Q operand of a step is one address for the
+// whole warp (a broadcast), the K operand a conflict-free full-width load; in P.V the roles swap (P[row][key] is the
+// broadcast, V[key][lane's dims] the full-width load).  Per lane 8 x BC/32 scores and 8 x D/32 output elements, i.e. far
+// fewer registers than the thread-tile form above needs at large head dims (179 against 255 at D = 256), which is
+// where it wins: 37.5 against 32.0 TFLOP/s at B2 S2048 H16 D256.  At D <= 192 it loses (D = 128: 35 against 46): the
+// broadcast loads are not as cheap as one shared-memory cycle, and with 8 + BC/32 loads per 8 x BC/32 x 4 FMAs the
+// kernel is as shared-memory-bound as the other form.  P goes through shared memory, but each warp reads back only the
+// rows it wrote.  The contract is the one stated at the top of this file.
+template <int D, int BC>
+__global__ void __launch_bounds__(256) fwd_fp32_lane_kernel(const Fp32Params p) {
+  constexpr int kThreads = 256;
+  constexpr int BR = 64;            // query rows per CTA
+  constexpr int R = 8;              // ... per warp
+  constexpr int C = BC / 32;        // keys per lane and block: lane, lane + 32, ...
+  constexpr int VW = (D % 128 == 0) ? 4 : (D % 64 == 0) ? 2 : 1;  // floats per vector of the lane's share of O / V
+  constexpr int NV = D / (32 * VW);                               // such vectors per lane: dims lane*VW + 32*VW*i
+  constexpr int LD = D + 4;
+  constexpr int LDP = BC + 4;
+  extern __shared__ float4 smemF4[];
+  float* sQ = reinterpret_cast<float*>(smemF4);
+  float* sK = sQ + BR * LD;
+  float* sV = sK + BC * LD;
+  float* sP = sV + BC * LD;
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int hkv = h / p.group;
+  long long qRow0, kvRow0;
+  int sq, skv;
+  if (p.cuQ != nullptr) {
+    qRow0 = p.cuQ[b];
+    sq = p.cuQ[b + 1] - p.cuQ[b];
+    kvRow0 = p.cuKV[b];
+    skv = p.cuKV[b + 1] - p.cuKV[b];
+  } else {
+    sq = p.seqLenQ;
+    skv = p.seqLenKV;
+    qRow0 = (long long)b * sq;
+    kvRow0 = (long long)b * skv;
+  }
+  const int numTilesQ = gridDim.x;
+  const int tileIdx = p.causal ? (numTilesQ - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // heavy causal tiles first
+  const int q0 = tileIdx * BR;
+  if (q0 >= sq || skv <= 0) return;
+  const int qEnd = min(q0 + BR, sq);
+  int nblk = (skv + BC - 1) / BC;
+  if (p.causal) nblk = min(nblk, (qEnd + BC - 1) / BC);
+
+  const long long qStride = (long long)p.headsQ * D;
+  const long long kvStride = (long long)p.headsKV * D;
+  const float* gQ = p.Q + (long long)h * D;
+  const float* gK = p.K + (long long)hkv * D;
+  const float* gV = p.V + (long long)hkv * D;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = warp * R;  // first row of this warp inside the tile
+
+  load_tile<D, BR, LD, kThreads>(sQ, gQ, qRow0 + q0, qRow0 + sq, qStride);
+  load_tile<D, BC, LD, kThreads>(sK, gK, kvRow0, kvRow0 + skv, kvStride);
+  cp_async_commit();
+
+  float o[R][NV * VW];
+  float m[R], l[R];
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV * VW; i++) o[r][i] = 0.f;
+  }
+  const float c = p.scaleLog2;
+
+  for (int j = 0; j < nblk; j++) {
+    const int kbase = j * BC;
+    load_tile<D, BC, LD, kThreads>(sV, gV, kvRow0 + kbase, kvRow0 + skv, kvStride);
+    cp_async_commit();
+    cp_async_wait<1>();  // Q and K(j) have landed
+    __syncthreads();
+
+    // ---- S = Q K^T: rows row0 .. row0+7, keys lane + 32*i
+    float s[R][C];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+#pragma unroll
+      for (int i = 0; i < C; i++) s[r][i] = 0.f;
+    }
+#pragma unroll 2
+    for (int d4 = 0; d4 < D / 4; d4++) {
+      float4 k[C];
+#pragma unroll
+      for (int i = 0; i < C; i++) k[i] = *reinterpret_cast<const float4*>(sK + (lane + 32 * i) * LD + d4 * 4);
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const float4 q = *reinterpret_cast<const float4*>(sQ + (row0 + r) * LD + d4 * 4);  // one address per warp
+#pragma unroll
+        for (int i = 0; i < C; i++) {
+          s[r][i] = fmaf(q.x, k[i].x, s[r][i]);
+          s[r][i] = fmaf(q.y, k[i].y, s[r][i]);
+          s[r][i] = fmaf(q.z, k[i].z, s[r][i]);
+          s[r][i] = fmaf(q.w, k[i].w, s[r][i]);
+        }
+      }
+    }
+
+    // ---- mask + online softmax; every lane ends up with the row's maximum, the row sum stays split over the lanes
+    const bool needMask = (kbase + BC > skv) || (p.causal && (kbase + BC - 1 > q0));
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      const int qpos = q0 + row0 + r;
+      if (needMask) {
+        int lim = skv - kbase;
+        if (p.causal) lim = min(lim, qpos - kbase + 1);
+#pragma unroll
+        for (int i = 0; i < C; i++) {
+          if (lane + 32 * i >= lim) s[r][i] = -INFINITY;
+        }
+      }
+      float mx = s[r][0];
+#pragma unroll
+      for (int i = 1; i < C; i++) mx = fmaxf(mx, s[r][i]);
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float mNew = fmaxf(m[r], mx);
+      const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
+      const float scale = (m[r] == -INFINITY) ? 0.f : ex2((m[r] - mUse) * c);
+      m[r] = mNew;
+      const float negMc = -mUse * c;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < C; i++) {
+        const float pv = ex2(fmaf(s[r][i], c, negMc));
+        sum += pv;
+        sP[(row0 + r) * LDP + lane + 32 * i] = pv;
+      }
+      l[r] = l[r] * scale + sum;
+#pragma unroll
+      for (int i = 0; i < NV * VW; i++) o[r][i] *= scale;
+    }
+
+    cp_async_wait<0>();  // V(j) has landed
+    __syncthreads();     // ... for everybody, nobody still reads K(j), and this warp's P rows are visible to its lanes
+    if (j + 1 < nblk) {
+      load_tile<D, BC, LD, kThreads>(sK, gK, kvRow0 + kbase + BC, kvRow0 + skv, kvStride);
+    }
+    cp_async_commit();
+
+    // ---- O += P V: P[row][key] is one address per warp, V[key][lane's dims] the full-width load
+#pragma unroll 2
+    for (int k4 = 0; k4 < BC / 4; k4++) {
+      float4 pr[R];
+#pragma unroll
+      for (int r = 0; r < R; r++) pr[r] = *reinterpret_cast<const float4*>(sP + (row0 + r) * LDP + k4 * 4);
+#pragma unroll
+      for (int kk = 0; kk < 4; kk++) {
+        float v[NV * VW];
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+          const float* src = sV + (k4 * 4 + kk) * LD + lane * VW + 32 * VW * i;
+          if constexpr (VW == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(src);
+            v[i * 4 + 0] = t.x;
+            v[i * 4 + 1] = t.y;
+            v[i * 4 + 2] = t.z;
+            v[i * 4 + 3] = t.w;
+          } else if constexpr (VW == 2) {
+            const float2 t = *reinterpret_cast<const float2*>(src);
+            v[i * 2 + 0] = t.x;
+            v[i * 2 + 1] = t.y;
+          } else {
+            v[i] = *src;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const float pw = (kk == 0) ? pr[r].x : (kk == 1) ? pr[r].y : (kk == 2) ? pr[r].z : pr[r].w;
+#pragma unroll
+          for (int i = 0; i < NV * VW; i++) o[r][i] = fmaf(pw, v[i], o[r][i]);
+        }
+      }
+    }
+    __syncthreads();  // V(j) and P are free again
+  }
+  cp_async_wait<0>();
+
+  // ---- normalise and store: lane writes its dims of each of the warp's rows
+#pragma unroll
+  for (int r = 0; r < R; r++) {
+    float sum = l[r];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float inv = (sum > 0.f) ? (1.f / sum) : 0.f;
+    const int qpos = q0 + row0 + r;
+    if (qpos < sq) {
+      float* dst = p.O + (qRow0 + qpos) * qStride + (long long)h * D;
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        float* d = dst + lane * VW + 32 * VW * i;
+        if constexpr (VW == 4) {
+          *reinterpret_cast<float4*>(d) = make_float4(o[r][i * 4] * inv, o[r][i * 4 + 1] * inv, o[r][i * 4 + 2] * inv,
+                                                      o[r][i * 4 + 3] * inv);
+        } else if constexpr (VW == 2) {
+          *reinterpret_cast<float2*>(d) = make_float2(o[r][i * 2] * inv, o[r][i * 2 + 1] * inv);
+        } else {
+          *d = o[r][i] * inv;
+        }
+      }
+    }
+  }
+}
+
+template <int D, int BC>
+int launch_lane(const FwdProblem& pr) {
+  constexpr int LD = D + 4;
+  constexpr int kSmem = (64 * LD + 2 * BC * LD + 64 * (BC + 4)) * (int)sizeof(float);
+  static_assert(kSmem <= 227 * 1024, "shared memory");
+  auto kernel = fwd_fp32_lane_kernel<D, BC>;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return kCudaError;
+  static std::once_flag once[64];
+  static cudaError_t attrErr[64];
+  std::call_once(once[device], [&] {
+    attrErr[device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  });
+  if (attrErr[device] != cudaSuccess) {
+    set_error_string("cudaFuncSetAttribute(%d bytes): %s", kSmem, cudaGetErrorString(attrErr[device]));
+    return kCudaError;
+  }
+  Fp32Params p;
+  p.Q = static_cast<const float*>(pr.Q);
+  p.K = static_cast<const float*>(pr.K);
+  p.V = static_cast<const float*>(pr.V);
+  p.O = static_cast<float*>(pr.O);
+  p.cuQ = pr.cuQ;
+  p.cuKV = pr.cuKV;
+  p.seqLenQ = pr.seqLenQ;
+  p.seqLenKV = pr.seqLenKV;
+  p.headsQ = pr.headsQ;
+  p.headsKV = pr.headsKV;
+  p.group = pr.headsQ / pr.headsKV;
+  p.causal = pr.causal;
+  p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)D));
+  dim3 grid((unsigned)((pr.seqLenQ + 63) / 64), (unsigned)pr.headsQ, (unsigned)pr.batch);
+  kernel<<<grid, 256, kSmem, pr.stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error_string("fp32 kernel launch failed: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  return kOk;
+}
+
 template <int D, int BR>
 int launch(const FwdProblem& pr) {
   constexpr int LD = D + 4;
@@ -404,7 +657,9 @@ int launch_fwd_fp32(const FwdProblem& pr) {
 #endif
 #if TFA_HAVE_HD256
     case 256:
-      return fp32::launch<256, 64>(pr);
+      // the warp-rows / lane-columns form: 37.5 against 32.0 TFLOP/s at B2 S2048 H16 (the thread-tile form sits at 255
+      // registers there); at every other head dim the thread-tile form is the faster one (128: 46 against 35)
+      return fp32::launch_lane<256, 64>(pr);
 #endif
     default:
       break;
