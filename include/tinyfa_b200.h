@@ -85,7 +85,8 @@ int tfa_b200_device_status(int* site);
 /*
  * Tuning / debugging knobs (process-wide).  No counterpart in the reference, whose tile table is fixed
  * at compile time (csrc/flash_attn/config.cuh:133-272).
- *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto / never / always
+ *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto (short query blocks and
+ *                      causal problems) / never / always
  *   "split_kv" -1/0/n  split-KV path for short query blocks (seqQ * group <= 16): auto / never / exactly n splits
  *   "solo64" 0/1       head dims 32 / 64: two-tile CTAs, one per SM / one-tile CTAs, two per SM (the default)
  *   "work_order" -1/0/n  order in which the persistent kernel hands out (query tile pair, head, batch) items:
