@@ -88,6 +88,7 @@ int tfa_b200_device_status(int* site);
  *   "pack_gqa" -1/0/1  interleave the Q heads of a KV group into one 128-row tile: auto (short query blocks and
  *                      causal problems) / never / always
  *   "split_kv" -1/0/n  split-KV path for short query blocks (seqQ * group <= 16): auto / never / exactly n splits
+ *   "narrow_mma" 0/1   head dims 32 / 96: MMAs of the padded width (64 / 128) / MMAs shaped for the head dim (the default)
  *   "solo64" 0/1       head dims 32 / 64: two-tile CTAs, one per SM / one-tile CTAs, two per SM (the default)
  *   "work_order" -1/0/n  order in which the persistent kernel hands out (query tile pair, head, batch) items:
  *                      auto (causal: heaviest pairs first inside chunks of heads whose K/V fit a quarter of L2;

@@ -72,6 +72,8 @@ static std::atomic<int> g_optWorkOrder{-1};  // -1 auto, 0 pair index fastest, n
 static std::atomic<int> g_epoch{1};
 
 int option_work_order() { return g_optWorkOrder.load(); }
+static std::atomic<int> g_optNarrowMma{1};
+int option_narrow_mma() { return g_optNarrowMma.load(); }
 static std::atomic<int> g_optSolo64{1};  // head dims 32 / 64: one-tile CTAs, two per SM (measured 4-10 % faster than the two-tile form)
 int option_solo64() { return g_optSolo64.load(); }
 
@@ -552,6 +554,10 @@ extern "C" int tfa_b200_set_option(const char* name, int value) {
   }
   if (strcmp(name, "split_kv") == 0) {
     g_optSplitKv.store(value < 0 ? -1 : value);
+    return kOk;
+  }
+  if (strcmp(name, "narrow_mma") == 0) {
+    g_optNarrowMma.store(value ? 1 : 0);
     return kOk;
   }
   if (strcmp(name, "solo64") == 0) {

@@ -429,11 +429,15 @@ __device__ __forceinline__ bool make_work(const TcParams& p, int idx, Work& w) {
 // fixed-length speed; the masking code 8 % at head dim 64 and nothing at 128 / 256, so mode 2 is only built for
 // the 64 kernel).
 constexpr int kModeFixed = 0, kModeVarlen = 1, kModeFixedNoMask = 2;
-template <int HDP, bool kBf16, int kMode, bool kSolo = false>
+// kHD: the head dim the MMAs are shaped for.  The tiles in shared memory are always HDP wide (64-element slabs, TMA
+// zero-fills past the true head dim); with kHD < HDP (32 in the 64-wide kernel, 96 in the 128-wide one) Q.K^T stops
+// after kHD / 16 k-steps, P.V produces kHD output columns, and the rescale and output passes touch kHD columns.
+template <int HDP, bool kBf16, int kMode, bool kSolo = false, int kHD = HDP>
 __global__ void __launch_bounds__(kSolo ? kThreadsSolo : kThreads, kSolo ? 2 : 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
   static_assert(!kSolo || HDP == 64, "the one-tile, two-CTAs-per-SM form exists for padded head dim 64 only");
+  static_assert(kHD == HDP || (HDP == 64 && kHD == 32) || (HDP == 128 && kHD == 96), "MMA head dim");
   using C = typename std::conditional<kSolo, CfgSolo64, Cfg<HDP>>::type;
   constexpr int NT = C::kNT;
   // warp roles: softmax warps [0, 4 * NT'), epilogue warps, the two MMA-issuing warps, the loading warp
@@ -636,7 +640,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tc_fence_after();
           const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll 1
-          for (int ch = 0; ch < HDP / 16; ch++) {  // 16 columns at a time: the scores of this block stay in registers
+          for (int ch = 0; ch < kHD / 16; ch++) {  // 16 columns at a time: the scores of this block stay in registers
             uint32_t o[16];
             ptx::tmem_ld_32x32b_x16(tO + ch * 16, o);
             ptx::tmem_wait_ld();
@@ -701,12 +705,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                                               ((w.qRow0 + qpos) * p.headsQ + head) * (long long)p.headDim);
         const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll
-        for (int ch = 0; ch < HDP / 32; ch++) {
+        for (int ch = 0; ch < kHD / 32; ch++) {
           uint32_t o[32];
           ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
           ptx::tmem_wait_ld();
           ptx::tmem_ld_fence(o);
-          if (ch == HDP / 32 - 1) {
+          if (ch == kHD / 32 - 1) {
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(kBarOFree + t));
@@ -769,12 +773,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                                               ((w.qRow0 + qpos) * p.headsQ + head) * (long long)p.headDim);
         const uint32_t tO = tmem + laneOff + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll
-        for (int ch = 0; ch < HDP / 32; ch++) {
+        for (int ch = 0; ch < kHD / 32; ch++) {
           uint32_t o[32];
           ptx::tmem_ld_32x32b_x32(tO + ch * 32, o);
           ptx::tmem_wait_ld();
           ptx::tmem_ld_fence(o);
-          if (ch == HDP / 32 - 1) {  // O is in registers: the next item's first P.V may overwrite the accumulator
+          if (ch == kHD / 32 - 1) {  // O is in registers: the next item's first P.V may overwrite the accumulator
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(kBarOFree + t));
@@ -800,7 +804,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // ============================================================== MMA issue
       const int fmt = kBf16 ? 1 : 0;
       const uint32_t idQK = ptx::instr_desc_f16(fmt, kBlockM, kBlockN, 0, 0);
-      const uint32_t idPV = ptx::instr_desc_f16(fmt, kBlockM, HDP, 0, 1);
+      const uint32_t idPV = ptx::instr_desc_f16(fmt, kBlockM, kHD, 0, 1);
       // K-major operands (Q, K): rows of 128 bytes, 8-row groups 1024 bytes apart.
       const uint64_t descK = ptx::smem_desc_sw128(16, 1024);
       // MN-major operand (V, head dim contiguous): 64-wide slabs kTileBytes/kSub apart, 8-key groups 1024 bytes apart.
@@ -818,8 +822,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const uint32_t kLo = kLoT | (kAddr >> 4);
         const uint32_t dS = dRegion + (uint32_t)((blk & 1) * C::kSPosStride);
 #pragma unroll
-        for (int k2 = 0; k2 < HDP / 32; k2++) {
-          const int kk = part * (HDP / 32) + k2;
+        for (int k2 = 0; k2 < kHD / 32; k2++) {
+          const int kk = part * (kHD / 32) + k2;
           const uint32_t off = (uint32_t)((kk >> 2) * kSubTileBytes + (kk & 3) * 32) >> 4;
           ptx::mma_ss_lohi(dS, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
         }

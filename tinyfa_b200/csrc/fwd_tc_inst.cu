@@ -31,6 +31,7 @@ int* device_work_counter(int device, cudaStream_t stream, int* rc, CUtensorMap**
 int launch_patch_varlen_maps(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, CUtensorMap* out,
                              const int* cuQ, const int* cuKV, int batch, cudaStream_t stream);  // c_abi.cu
 int device_num_sms(int device);       // c_abi.cu
+int option_narrow_mma();              // c_abi.cu: MMAs shaped for head dims 32 / 96 inside the 64- / 128-wide kernels
 int option_solo64();                  // c_abi.cu: one-tile CTAs, two per SM, for head dims 32 / 64
 int option_work_order();              // c_abi.cu: -1 auto, 0 pair index fastest, n > 0 chunk width
 
@@ -63,19 +64,32 @@ static int make_map(CUtensorMap* m, const void* base, long long batches, long lo
 int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   using C = tc::Cfg<TFA_HDP>;
   const bool varlen = (pr.cuQ != nullptr);
-  auto kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen>
-                       : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed>;
+  constexpr bool kBf = (TFA_BF16 != 0);
+  auto kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeVarlen> : tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed>;
   bool solo = false;  // one Q tile per CTA, two CTAs per SM (padded head dim 64 only)
   int kNT = C::kNT, smemBytes = C::kSmemBytes, threads = tc::kThreads;
+#if TFA_HDP == 128
+  // head dim 96 has MMAs of its own shape in the 128-wide kernel (6 of 8 k-steps, 96 output columns)
+  if (pr.headDim == 96 && option_narrow_mma() != 0) {
+    kernel = varlen ? tc::fwd_tc_kernel<128, kBf, tc::kModeVarlen, false, 96> : tc::fwd_tc_kernel<128, kBf, tc::kModeFixed, false, 96>;
+  }
+#endif
 #if TFA_HDP == 64
   // nothing to mask: not causal, and the key length fills its last 128-key block
   const bool noMask = !varlen && !pr.causal && pr.seqLenKV % tc::kBlockN == 0;
-  if (noMask) kernel = tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>;
+  if (noMask) kernel = tc::fwd_tc_kernel<64, kBf, tc::kModeFixedNoMask>;
   solo = option_solo64() != 0;
   if (solo) {
-    kernel = varlen ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen, true>
-                    : (noMask ? tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask, true>
-                              : tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed, true>);
+    const bool narrow = (pr.headDim == 32 && option_narrow_mma() != 0);  // head dim 32: 2 of 4 k-steps, 32 output columns
+    if (narrow) {
+      kernel = varlen ? tc::fwd_tc_kernel<64, kBf, tc::kModeVarlen, true, 32>
+                      : (noMask ? tc::fwd_tc_kernel<64, kBf, tc::kModeFixedNoMask, true, 32>
+                                : tc::fwd_tc_kernel<64, kBf, tc::kModeFixed, true, 32>);
+    } else {
+      kernel = varlen ? tc::fwd_tc_kernel<64, kBf, tc::kModeVarlen, true>
+                      : (noMask ? tc::fwd_tc_kernel<64, kBf, tc::kModeFixedNoMask, true>
+                                : tc::fwd_tc_kernel<64, kBf, tc::kModeFixed, true>);
+    }
     kNT = 1;
     smemBytes = tc::CfgSolo64::kSmemBytes;
     threads = tc::kThreadsSolo;
@@ -88,17 +102,19 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   static cudaError_t attrErr[64];
   if (device < 0 || device >= 64) return kBadArgument;
   std::call_once(once[device], [&] {
-    attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (attrErr[device] == cudaSuccess) {
-      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    }
+    auto bigAttr = [&](auto k) {
+      if (attrErr[device] != cudaSuccess) return;
+      attrErr[device] = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    };
+    attrErr[device] = cudaSuccess;
+    bigAttr(tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed>);
+    bigAttr(tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeVarlen>);
+#if TFA_HDP == 128
+    bigAttr(tc::fwd_tc_kernel<128, kBf, tc::kModeFixed, false, 96>);
+    bigAttr(tc::fwd_tc_kernel<128, kBf, tc::kModeVarlen, false, 96>);
+#endif
 #if TFA_HDP == 64
-    if (attrErr[device] == cudaSuccess) {
-      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    }
+    bigAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeFixedNoMask>);
     // the two-CTAs-per-SM form: 99 KB each, and the largest shared-memory carve-out so that two fit
     auto soloAttr = [&](auto k) {
       if (attrErr[device] != cudaSuccess) return;
@@ -107,9 +123,12 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
         attrErr[device] = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
       }
     };
-    soloAttr(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixed, true>);
-    soloAttr(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeVarlen, true>);
-    soloAttr(tc::fwd_tc_kernel<TFA_HDP, (TFA_BF16 != 0), tc::kModeFixedNoMask, true>);
+    soloAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeFixed, true>);
+    soloAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeVarlen, true>);
+    soloAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeFixedNoMask, true>);
+    soloAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeFixed, true, 32>);
+    soloAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeVarlen, true, 32>);
+    soloAttr(tc::fwd_tc_kernel<64, kBf, tc::kModeFixedNoMask, true, 32>);
 #endif
   });
   if (attrErr[device] != cudaSuccess) {
