@@ -75,5 +75,58 @@ def test_random_packed_batches(seed):
     assert err <= cases.MAXABS_TOL[dtype], (dtype, sq, skv, Hq, Hkv, D, causal, err)
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_random_long_causal_gqa_and_small_head_dims(seed):
+    """Shapes that reach the forms picked by the dispatcher for them: causal GQA with the group's heads interleaved
+    into one tile (group sizes with and without a power-of-two part, lengths of several tiles), head dims 32 / 64 in
+    one-tile CTAs, head dims 32 / 96 with MMAs of their own shape, the heaviest-first work order with more items than
+    CTAs; packed batches through the C ABI with the totals left to the device (-1)."""
+    from tinyfa_b200 import _lib
+
+    rng = np.random.default_rng(3000 + seed)
+    dtype = ("bf16", "fp16")[seed % 2]
+    D = (32, 64, 96, 128, 192, 256)[seed % 6]
+    group = (1, 2, 3, 4, 6, 8)[int(rng.integers(0, 6))]
+    Hkv = int(rng.integers(1, 3))
+    Hq = Hkv * group
+    causal = bool(seed % 3)
+    if seed % 4 != 3:
+        B = int(rng.integers(1, 3))
+        Sq = int(rng.integers(300, 1400))
+        Skv = Sq if rng.integers(0, 2) else int(rng.integers(300, 1400))
+        Q = rng.normal(0, 1, (B, Sq, Hq, D)).astype(np.float32)
+        K = rng.normal(0, 1, (B, Skv, Hkv, D)).astype(np.float32)
+        V = rng.normal(0, 1, (B, Skv, Hkv, D)).astype(np.float32)
+        Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+        O = tf.flash_attn_forward(Qd, Kd, Vd, is_causal=causal)
+        ref = ao.fixed(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), causal, "f64")
+        what = (dtype, B, Sq, Skv, Hq, Hkv, D, causal)
+    else:
+        nseq = int(rng.integers(2, 5))
+        sq = [int(rng.integers(1, 900)) for _ in range(nseq)]
+        skv = [int(rng.integers(1, 900)) for _ in range(nseq)]
+        cu_q = np.concatenate([[0], np.cumsum(sq)]).astype(np.int32)
+        cu_kv = np.concatenate([[0], np.cumsum(skv)]).astype(np.int32)
+        Q = rng.normal(0, 1, (int(cu_q[-1]), Hq, D)).astype(np.float32)
+        K = rng.normal(0, 1, (int(cu_kv[-1]), Hkv, D)).astype(np.float32)
+        V = rng.normal(0, 1, (int(cu_kv[-1]), Hkv, D)).astype(np.float32)
+        Qd, Kd, Vd = (torch.from_numpy(x).to(DT[dtype]).cuda() for x in (Q, K, V))
+        cq, ck = torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_kv).cuda()
+        O = torch.zeros_like(Qd)
+        code = {"fp16": 1, "bf16": 2}[dtype]
+        rc = _lib.load().tfa_b200_fwd_varlen(Qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), O.data_ptr(), cq.data_ptr(),
+                                             ck.data_ptr(), code, nseq, max(sq), max(skv), -1, -1, Hq, Hkv, D, int(causal),
+                                             torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        ref = ao.varlen(Qd.float().cpu().numpy(), Kd.float().cpu().numpy(), Vd.float().cpu().numpy(), cu_q, cu_kv, causal,
+                        "f64")
+        what = (dtype, sq, skv, Hq, Hkv, D, causal)
+    out = O.float().cpu().numpy()
+    assert np.isfinite(out).all(), what
+    err = np.abs(out - ref).max()
+    assert err <= cases.MAXABS_TOL[dtype], (what, err)
+
+
 def test_no_bounded_wait_gave_up_during_fuzzing():
     tf.device_status()
