@@ -68,8 +68,16 @@ constexpr int kBlockM = 128;  // query rows per tile = TMEM lanes
 constexpr int kBlockN = 128;  // keys per KV block
 constexpr int kThreads = 512;
 constexpr int kIssuerB = 15;  // warp that issues the MMAs of Q tile 1 (warp 12 issues those of tile 0)
-constexpr int kEmuPeriod = 8;  // of every kEmuPeriod pairs of exponentials ...
-constexpr int kEmuCount = 1;   // ... this many are evaluated on the FMA pipe instead of the MUFU
+// Of every kEmuPeriod pairs of exponentials, the first kEmuCount are evaluated on the FMA pipe instead of the MUFU: pairs
+// 0, 16, 32 and 48 of the 64 of a row and key block, i.e. the first pair of each 32-column quarter.  Measured on the
+// benchmark shape (bf16 / fp16 non-causal, interleaved A/B of one build per pattern): none 961, 1 of 64 963, 2 of 64 991,
+// 3 of 64 1071, **1 of 16 1187 / 1104**, 3 of 32 1043, 1 of 8 1055 / 1003, 1 of 4 942 TFLOP/s; the same four pairs moved
+// to positions 8 or 15 of each quarter 1047 / 1073, all four in the first quarter 1014, five per block 1076.  The
+// optimum is narrow and belongs to the instruction schedule the compiler finds for this exact mix (the FMA-pipe
+// sequence is a long dependent chain that it hides behind the MUFU instructions of the pairs around it), not to a
+// pipe-throughput model: by throughput alone 2-3 of 8 pairs would pay.
+constexpr int kEmuPeriod = 16;
+constexpr int kEmuCount = 1;
 // Register split of the 64 K registers of an SM between the role groups (8 + 4 + 4 warps).
 constexpr int kRegsSoftmax = 176;
 constexpr int kRegsEpilogue = 96;
@@ -281,12 +289,12 @@ __device__ __forceinline__ float2 fadd2_rm(float2 a, float2 b) {  // round towar
 }
 
 // exp2 on the FMA pipe for a pair of values (the MUFU unit is the co-bottleneck of this kernel: 16 ex2/clk/SM
-// against 128x128 exponentials per tile-block).  x = floor(x) + f; 2^f by a minimax polynomial with p(0) = 1;
-// 2^floor(x) by adding to the exponent field.  The magic constant 1.5*2^23 makes the low mantissa bits of t hold
-// floor(x); x is clamped at -127.  The result feeds the 16-bit P, so the polynomial only has to stay below that
-// type's rounding: a cubic for bf16 (max relative error 8.6e-5 against 2^-9), a quartic for fp16 (2.9e-6 against
-// 2^-12; with the cubic the mean output error was 3.5 % above the reference kernels' on the fp16 benchmark shape).
-template <bool kQuartic>
+// against 128x128 exponentials per tile-block).  x = floor(x) + f; 2^f by a minimax cubic with p(0) = 1 (max relative
+// error 8.6e-5); 2^floor(x) by adding to the exponent field.  The magic constant 1.5*2^23 makes the low mantissa bits
+// of t hold floor(x); x is clamped at -127.  The result feeds the 16-bit P: 8.6e-5 is far below bf16's rounding (2^-9)
+// and, on one value in sixteen, adds 0.3 % to the rms error of an fp16 P (2^-12).  (A quartic, 2.9e-6, was measured for
+// fp16: no difference in the output error - that is set by the stale row maxima, see kRescaleLog2 - and it does not get
+// the schedule the cubic gets: 999 against 1104 TFLOP/s.)
 __device__ __forceinline__ float2 ex2_fma2(float2 x) {
   const float kMagic = 12582912.f;
   x.x = fmaxf(x.x, -127.f);
@@ -294,15 +302,8 @@ __device__ __forceinline__ float2 ex2_fma2(float2 x) {
   const float2 t = fadd2_rm(x, make_float2(kMagic, kMagic));
   const float2 xi = fadd2(t, make_float2(-kMagic, -kMagic));
   const float2 f = ffma2(xi, make_float2(-1.f, -1.f), x);
-  float2 p;
-  if constexpr (kQuartic) {
-    p = ffma2(make_float2(0.013425155f, 0.013425155f), f, make_float2(0.052245375f, 0.052245375f));
-    p = ffma2(p, f, make_float2(0.24127856f, 0.24127856f));
-    p = ffma2(p, f, make_float2(0.69304514f, 0.69304514f));
-  } else {
-    p = ffma2(make_float2(0.07706704f, 0.07706704f), f, make_float2(0.22764499f, 0.22764499f));
-    p = ffma2(p, f, make_float2(0.69511679f, 0.69511679f));
-  }
+  float2 p = ffma2(make_float2(0.07706704f, 0.07706704f), f, make_float2(0.22764499f, 0.22764499f));
+  p = ffma2(p, f, make_float2(0.69511679f, 0.69511679f));
   p = ffma2(p, f, make_float2(1.f, 1.f));
   p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
   p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
@@ -596,14 +597,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         // Exponentials of one 32-key quarter: 16 pairs -> 16 packed 16-bit words, plus their (unrounded) sum.
         const float2 c2 = make_float2(c, c);
-        auto expQuarter = [&](const uint32_t(&vq)[32], float negMc, uint32_t(&dst)[16], float2& sum) {
+        auto expQuarter = [&](const uint32_t(&vq)[32], float negMc, uint32_t(&dst)[16], float2& sum, const int quarter) {
           const float2 negMc2 = make_float2(negMc, negMc);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float2 x = make_float2(__uint_as_float(vq[i]), __uint_as_float(vq[i + 1]));
             x = ffma2(x, c2, negMc2);
-            if (((i >> 1) % kEmuPeriod) < kEmuCount) {  // compile-time pattern: this pair goes to the FMA pipe
-              x = ex2_fma2<!kBf16>(x);
+            if (((quarter * 16 + (i >> 1)) % kEmuPeriod) < kEmuCount) {  // compile-time pattern: this pair goes to the FMA pipe
+              x = ex2_fma2(x);
             } else {
               x.x = ex2(x.x);
               x.y = ex2(x.y);
@@ -663,11 +664,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int half = 0; half < 2; half++) {
           if (half == 0) {
-            expQuarter(v[0], negMc, pkA, sum2);
-            expQuarter(v[1], negMc, pkB, sum2);
+            expQuarter(v[0], negMc, pkA, sum2, 0);
+            expQuarter(v[1], negMc, pkB, sum2, 1);
           } else {
-            expQuarter(v[2], negMc, pkA, sum2);
-            expQuarter(v[3], negMc, pkB, sum2);
+            expQuarter(v[2], negMc, pkA, sum2, 2);
+            expQuarter(v[3], negMc, pkB, sum2, 3);
           }
           if constexpr (kVarlen) {
            if (half == 0 && kbase + kBlockN > w.skv) {
