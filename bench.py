@@ -78,13 +78,13 @@ STRONG_WORKLOADS = ("bf16_causal_gqa_b4_s8192_h32_8_d128", "bf16_causal_varlen_g
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (decode batch 64: the batch-8 capture scaled by units processed; traffic grows in proportion to batch).
 NCU_TRAFFIC_BYTES = {
-    "bf16_noncausal_b2_s4096_h32_d128": 246329088,
-    "bf16_causal_b2_s4096_h32_d128": 263884544,
-    "bf16_causal_varlen_gqa_16seq_h32_8_d128": 1348863488,
-    "bf16_causal_gqa_b4_s8192_h32_8_d128": 643794688,
-    "fp16_causal_b8_s2048_h16_d64": 115061248,
-    "fp16_causal_b8_s2048_h16_d32": 52957696,
-    "fp16_causal_b8_s2048_h16_d96": 183778048,
+    "bf16_noncausal_b2_s4096_h32_d128": 247334144,
+    "bf16_causal_b2_s4096_h32_d128": 266387456,
+    "bf16_causal_varlen_gqa_16seq_h32_8_d128": 1343037184,
+    "bf16_causal_gqa_b4_s8192_h32_8_d128": 644488192,
+    "fp16_causal_b8_s2048_h16_d64": 115396096,
+    "fp16_causal_b8_s2048_h16_d32": 53254912,
+    "fp16_causal_b8_s2048_h16_d96": 184531200,
     "fp16_causal_b8_s2048_h16_d192": 384580864,
     "fp16_causal_b8_s2048_h16_d256": 523113216,
     "fp32_noncausal_b2_s4096_h32_d128": 518427392,
