@@ -76,6 +76,8 @@ static std::atomic<int> g_optNarrowMma{1};
 int option_narrow_mma() { return g_optNarrowMma.load(); }
 static std::atomic<int> g_optSolo64{1};  // head dims 32 / 64: one-tile CTAs, two per SM (measured 4-10 % faster than the two-tile form)
 int option_solo64() { return g_optSolo64.load(); }
+static std::atomic<int> g_optPairCta{-1};  // head dims 192 / 256, fixed length: clusters of two CTAs sharing every K/V block (-1 auto)
+int option_pair_cta() { return g_optPairCta.load(); }
 
 int next_epoch() { return (g_epoch.fetch_add(1) & 0x7FFFFF) + 1; }
 
@@ -562,6 +564,10 @@ extern "C" int tfa_b200_set_option(const char* name, int value) {
   }
   if (strcmp(name, "solo64") == 0) {
     g_optSolo64.store(value ? 1 : 0);
+    return kOk;
+  }
+  if (strcmp(name, "pair_cta") == 0) {
+    g_optPairCta.store(value < 0 ? -1 : (value ? 1 : 0));
     return kOk;
   }
   if (strcmp(name, "work_order") == 0) {

@@ -119,7 +119,8 @@ struct Cfg {
   static constexpr int kPPosStride = kTwoPos ? 128 : 0;                    // column offset of P for odd blocks
   static constexpr int kSRegion = kRot ? 192 : (kDblS ? 256 : 128);        // columns per tile for S / P
   static constexpr int kOCol0 = kRot ? 384 : 256;
-  static constexpr int kSmemBytes = (kNT * kQBufs + kStages) * kTileBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
+  static constexpr int kStageBytes = kTileBytes;         // one K/V ring stage
+  static constexpr int kSmemBytes = kNT * kQBufs * kTileBytes + kStages * kStageBytes + 2048 /*barriers, scales*/ + 1024 /*align*/;
 };
 
 // Head dim <= 64, second form: ONE Q tile per CTA and TWO CTAs per SM (8 warps each: 4 softmax warps that also
@@ -141,8 +142,50 @@ struct CfgSolo64 {
   static constexpr int kPPosStride = 128;
   static constexpr int kSRegion = 192;
   static constexpr int kOCol0 = 192;
-  static constexpr int kSmemBytes = (kNT * kQBufs + kStages) * kTileBytes + 2048 + 1024;
+  static constexpr int kStageBytes = kTileBytes;
+  static constexpr int kSmemBytes = kNT * kQBufs * kTileBytes + kStages * kStageBytes + 2048 + 1024;
 };
+
+// Head dims 192 / 256, pair form: a cluster of two CTAs on the two SMs of a TPC works on two neighbouring Q tiles of one
+// head (one tile each) and shares every K/V block: the MMAs are issued by rank 0 with cta_group::2 (M = 256), which
+// reads half of the B operand from each CTA's shared memory - keys [64 r, 64 r + 64) of the block for Q.K^T, half of
+// the head dim for P.V.  Each CTA therefore loads half of every K and V block: half the L2 -> shared-memory traffic
+// per FLOP of the one-tile form (which pulls 7-8 TB/s out of L2 at these head dims and is bound by it), and ring
+// stages of 32 KB instead of 64 / 48 KB, i.e. room for four or five of them.  Tensor memory as in the one-tile form:
+// two S buffers and O.  At head dim 192 each CTA's half of V is 96 columns, one and a half 64-element slabs: CTA r
+// loads the slabs at head-dim offsets {0, 128} (r = 0) or {64, 160} (r = 1) and the MMA uses the first 96 columns, so
+// that the O columns come out permuted in chunks of 32 (kColMap); the output pass undoes it.
+template <int HDP>
+struct CfgPair {
+  static_assert(HDP == 192 || HDP == 256, "pair form: head dims 192 and 256");
+  static constexpr int kSub = HDP / 64;
+  static constexpr int kTileBytes = kSub * kSubTileBytes;  // one 128-row Q tile
+  static constexpr int kNT = 1;
+  static constexpr int kQBufs = 1;
+  static constexpr int kStageBytes = 2 * kSubTileBytes;  // K: 64 keys x HDP (<= 32 KB); V: 128 keys x two 64-wide slabs
+  static constexpr int kStages = (HDP == 256) ? 4 : 5;
+  static constexpr int kTmemCols = 512;
+  static constexpr bool kRot = false;
+  static constexpr bool kDblS = true;
+  static constexpr bool kTwoPos = true;
+  static constexpr int kSPosStride = 128;
+  static constexpr int kPPosStride = 128;
+  static constexpr int kSRegion = 256;
+  static constexpr int kOCol0 = 256;
+  static constexpr int kSmemBytes = kTileBytes + kStages * kStageBytes + 2048 + 1024;
+};
+// head-dim offset of the 32-column chunk ch of O (pair form; identity except at head dim 192, see CfgPair)
+template <int HDP, bool kPair>
+__host__ __device__ constexpr int o_chunk_offset(int ch) {
+  if (kPair && HDP == 192) return ch == 0 ? 0 : ch == 1 ? 32 : ch == 2 ? 128 : ch == 3 ? 64 : ch == 4 ? 96 : 160;
+  return ch * 32;
+}
+// head-dim offset of the slab a (0 / 1) of V that CTA `rank` of a pair loads
+template <int HDP>
+__device__ __forceinline__ int v_slab_offset(int rank, int a) {
+  if (HDP == 192) return rank == 0 ? a * 128 : 64 + a * 96;
+  return rank * 128 + a * 64;
+}
 constexpr int kThreadsSolo = 256;  // two whole warpgroups (setmaxnreg is a warpgroup-wide instruction); warps 6 and 7 idle
 
 // Barrier slots (8 bytes each) inside the control block that follows the tiles.
@@ -164,7 +207,11 @@ enum Bar : int {
   kBarWorkEmpty = 30,  // [2]  every consumer has read the slot
   kBarKvFull = 32,     // [kStages <= 6]
   kBarKvEmpty = 38,    // [kStages <= 6]
-  kNumBars = 48,
+  // pair form only
+  kBarIdxFull = 48,    // [2]  rank 1: rank 0 has written the next work index into peerIdx[k & 1]
+  kBarIdxEmpty = 50,   // [2]  rank 0: rank 1 has read peerIdx[k & 1]
+  kBarOFreePair = 52,  // rank 0: the epilogue warps of both CTAs have read O of the item (8 arrivals)
+  kNumBars = 54,
 };
 
 constexpr int kWorkConsumers = 14;  // 8 softmax warps + 4 epilogue warps + 2 MMA-issuing threads
@@ -188,6 +235,7 @@ struct Ctl {
   uint32_t tmemBase;
   int failed;
   WorkSlot work[2];
+  int peerIdx[2];  // pair form, rank 1: work indices handed over by rank 0
 };
 
 struct WaitCtx {
@@ -203,6 +251,26 @@ __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, const Wa
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3FF) == 0) {
+      if (*c.failed) return;
+      const uint64_t now = ptx::global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2000000000ull) {
+        *c.failed = 1;
+        atomicExch(c.status, (c.epoch << 8) | site);
+        return;
+      }
+    }
+  }
+}
+
+// Same contract as wait_bar, with cluster-scope acquire: what the other CTA of a pair stored into this CTA's shared
+// memory before its arrival is visible afterwards.
+__device__ __forceinline__ void wait_bar_cluster(uint32_t bar, uint32_t parity, const WaitCtx& c, int site) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!ptx::mbar_try_wait_cluster(bar, parity)) {
     if ((++spins & 0x3FF) == 0) {
       if (*c.failed) return;
       const uint64_t now = ptx::global_timer_ns();
@@ -433,13 +501,16 @@ constexpr int kModeFixed = 0, kModeVarlen = 1, kModeFixedNoMask = 2;
 // kHD: the head dim the MMAs are shaped for.  The tiles in shared memory are always HDP wide (64-element slabs, TMA
 // zero-fills past the true head dim); with kHD < HDP (32 in the 64-wide kernel, 96 in the 128-wide one) Q.K^T stops
 // after kHD / 16 k-steps, P.V produces kHD output columns, and the rescale and output passes touch kHD columns.
-template <int HDP, bool kBf16, int kMode, bool kSolo = false, int kHD = HDP>
+// kPair: the CTA-pair form of head dims 192 / 256 (CfgPair): launched as clusters of two, fixed-length input only.
+template <int HDP, bool kBf16, int kMode, bool kSolo = false, int kHD = HDP, bool kPair = false>
 __global__ void __launch_bounds__(kSolo ? kThreadsSolo : kThreads, kSolo ? 2 : 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const TcParams p) {
   static_assert(!kSolo || HDP == 64, "the one-tile, two-CTAs-per-SM form exists for padded head dim 64 only");
   static_assert(kHD == HDP || (HDP == 64 && kHD == 32) || (HDP == 128 && kHD == 96), "MMA head dim");
-  using C = typename std::conditional<kSolo, CfgSolo64, Cfg<HDP>>::type;
+  static_assert(!kPair || (HDP >= 192 && kMode == kModeFixed && !kSolo), "pair form: head dims 192 / 256, fixed length");
+  using C = typename std::conditional<kPair, CfgPair<(kPair ? HDP : 256)>,
+                                      typename std::conditional<kSolo, CfgSolo64, Cfg<HDP>>::type>::type;
   constexpr int NT = C::kNT;
   // warp roles: softmax warps [0, 4 * NT'), epilogue warps, the two MMA-issuing warps, the loading warp
   constexpr int kSoftmaxWarps = kSolo ? 4 : 8;
@@ -456,20 +527,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* smem = smemRaw + (tileAddr - rawAddr);
   const uint32_t sQ = tileAddr;
   const uint32_t sKV = tileAddr + NT * C::kQBufs * C::kTileBytes;
-  Ctl* ctl = reinterpret_cast<Ctl*>(smem + (NT * C::kQBufs + NS) * C::kTileBytes);
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + NT * C::kQBufs * C::kTileBytes + NS * C::kStageBytes);
   const uint32_t barBase = ptx::smem_u32(&ctl->bars[0]);
   auto bar = [&](int slot) { return barBase + 8u * (uint32_t)slot; };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // pair form: rank in the cluster of two, and this CTA's / rank 0's barrier block seen through the cluster window
+  uint32_t rank = 0, barBase0 = barBase, barBasePeer = barBase;
+  if constexpr (kPair) {
+    rank = ptx::cluster_ctarank();
+    barBase0 = ptx::mapa(barBase, 0);
+    barBasePeer = ptx::mapa(barBase, rank ^ 1u);
+  }
+  auto bar0 = [&](int slot) { return barBase0 + 8u * (uint32_t)slot; };  // the barrier of rank 0 (cluster address)
+  (void)barBasePeer;
+  (void)bar0;
 
   if (threadIdx.x == 0) {
     for (int t = 0; t < 2; t++) {
       for (int u = 0; u < 2; u++) {
         ptx::mbar_init(bar(kBarQFull + 2 * t + u), 1);
         ptx::mbar_init(bar(kBarQEmpty + 2 * t + u), 1);
-        ptx::mbar_init(bar(kBarP0Ready + 2 * t + u), 4);
-        ptx::mbar_init(bar(kBarP1Ready + 2 * t + u), 4);
+        ptx::mbar_init(bar(kBarP0Ready + 2 * t + u), kPair ? 8 : 4);  // pair form: the softmax warps of both CTAs
+        ptx::mbar_init(bar(kBarP1Ready + 2 * t + u), kPair ? 8 : 4);
         ptx::mbar_init(bar(kBarSFull + 2 * t + u), 1);
         ptx::mbar_init(bar(kBarPvDone + 2 * t + u), 1);
       }
@@ -479,7 +560,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::mbar_init(bar(kBarOFree + t), 4);
       ptx::mbar_init(bar(kBarWorkFull + t), 1);
       ptx::mbar_init(bar(kBarWorkEmpty + t), kConsumers);
+      ptx::mbar_init(bar(kBarIdxFull + t), 1);
+      ptx::mbar_init(bar(kBarIdxEmpty + t), 1);
     }
+    ptx::mbar_init(bar(kBarOFreePair), 8);
     for (int s = 0; s < NS; s++) {
       ptx::mbar_init(bar(kBarKvFull + s), 1);
       ptx::mbar_init(bar(kBarKvEmpty + s), 2);  // one arrival per MMA-issuing thread
@@ -489,8 +573,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     ptx::fence_proxy_async_smem();
   }
   if (warp == kIssueWarpA) {
-    ptx::tmem_alloc(ptx::smem_u32(&ctl->tmemBase), C::kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (kPair) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&ctl->tmemBase), C::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&ctl->tmemBase), C::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   // tensor maps: the kernel arguments, or (packed input with totals only known on the device) maps in global memory
   const CUtensorMap* mapQ = &tmQ;
@@ -516,6 +605,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync();  // the other CTA's barriers are initialised before anyone arrives on them
   ptx::tc_fence_after();
   const uint32_t tmem = ctl->tmemBase;
   const WaitCtx wc{&ctl->failed, p.status, p.epoch};
@@ -688,7 +778,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + 2 * t + pSlot));
+          if (lane == 0) {
+            if constexpr (kPair) {  // the issuing thread of rank 0 waits for both CTAs' halves of the 256-row P
+              ptx::mbar_arrive_cluster(bar0((half == 0 ? kBarP0Ready : kBarP1Ready) + 2 * t + pSlot));
+            } else {
+              ptx::mbar_arrive(bar((half == 0 ? kBarP0Ready : kBarP1Ready) + 2 * t + pSlot));
+            }
+          }
         }
         l += sum2.x + sum2.y;
       }
@@ -782,9 +878,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (ch == kHD / 32 - 1) {  // O is in registers: the next item's first P.V may overwrite the accumulator
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar(kBarOFree + t));
+            if (lane == 0) {
+              ptx::mbar_arrive(bar(kBarOFree + t));
+              if constexpr (kPair) ptx::mbar_arrive_cluster(bar0(kBarOFreePair));
+            }
           }
-          if (valid && ch * 32 < p.headDim) {
+          const int hdOff = o_chunk_offset<HDP, kPair>(ch);  // a constant once the loop is unrolled
+          if (valid && hdOff < p.headDim) {
 #pragma unroll
             for (int g = 0; g < 4; g++) {
               uint4 q;
@@ -792,7 +892,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               q.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
               q.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
               q.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
-              dst[ch * 4 + g] = q;
+              dst[hdOff / 8 + g] = q;
             }
           }
         }
@@ -804,8 +904,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if ((warp == kIssueWarpA || warp == kIssueWarpB) && lane == 0) {
       // ============================================================== MMA issue
       const int fmt = kBf16 ? 1 : 0;
-      const uint32_t idQK = ptx::instr_desc_f16(fmt, kBlockM, kBlockN, 0, 0);
-      const uint32_t idPV = ptx::instr_desc_f16(fmt, kBlockM, kHD, 0, 1);
+      // pair form: M = 256 over the two CTAs
+      const uint32_t idQK = ptx::instr_desc_f16(fmt, kPair ? 2 * kBlockM : kBlockM, kBlockN, 0, 0);
+      const uint32_t idPV = ptx::instr_desc_f16(fmt, kPair ? 2 * kBlockM : kBlockM, kHD, 0, 1);
       // K-major operands (Q, K): rows of 128 bytes, 8-row groups 1024 bytes apart.
       const uint64_t descK = ptx::smem_desc_sw128(16, 1024);
       // MN-major operand (V, head dim contiguous): 64-wide slabs kTileBytes/kSub apart, 8-key groups 1024 bytes apart.
@@ -826,7 +927,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int k2 = 0; k2 < kHD / 32; k2++) {
           const int kk = part * (kHD / 32) + k2;
           const uint32_t off = (uint32_t)((kk >> 2) * kSubTileBytes + (kk & 3) * 32) >> 4;
-          ptx::mma_ss_lohi(dS, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
+          if constexpr (kPair) {  // this CTA's K slabs hold 64 keys: half the slab stride
+            const uint32_t offB = (uint32_t)((kk >> 2) * (kSubTileBytes / 2) + (kk & 3) * 32) >> 4;
+            ptx::mma_ss_lohi_pair(dS, qLo + off, kHi, kLo + offB, kHi, idQK, kk > 0 ? 1u : 0u);
+          } else {
+            ptx::mma_ss_lohi(dS, qLo + off, kHi, kLo + off, kHi, idQK, kk > 0 ? 1u : 0u);
+          }
+        }
+      };
+      // completion of everything issued so far -> barrier (pair form: the same barrier in both CTAs)
+      auto commit = [&](uint32_t b) {
+        if constexpr (kPair) {
+          ptx::tc_commit_pair(b, 3);
+        } else {
+          ptx::tc_commit(b);
         }
       };
       auto issuePV = [&](int blk, uint32_t vAddr, uint32_t firstAcc, int half) {  // firstAcc: accumulate flag of k-step 0
@@ -835,7 +949,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int k4 = 0; k4 < kBlockN / 32; k4++) {
           const int kk = half * (kBlockN / 32) + k4;
-          ptx::mma_ts_lohi(dO, aP + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, kk == 0 ? firstAcc : 1u);
+          if constexpr (kPair) {
+            ptx::mma_ts_lohi_pair(dO, aP + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, kk == 0 ? firstAcc : 1u);
+          } else {
+            ptx::mma_ts_lohi(dO, aP + kk * 8, vLo + ((kk * 2048) >> 4), vHi, idPV, kk == 0 ? firstAcc : 1u);
+          }
         }
       };
 
@@ -847,7 +965,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // the load.  A thread therefore never waits for a block it does not need, and the loader's arrival cannot be
       // counted for the stage's previous use because the loader has waited for that phase before re-using the stage.
       auto release = [&](int stage, bool used) {
-        if (used) ptx::tc_commit(bar(kBarKvEmpty + stage));
+        if (used) commit(bar(kBarKvEmpty + stage));
       };
       // The two issuers take strict turns (A: tile 0, B: tile 1, A, B, ...), which keeps the two tiles in
       // anti-phase: one tile's softmax runs while the other tile's MMAs run.  Without the turn token the two
@@ -865,7 +983,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
         if (idx < 0 || *wc.failed) break;
         if (w.nmax == 0) continue;
-        const int n = (t < NT) ? w.nblk[t] : 0;
+        // pair form: rank 1 issues nothing (its loop only keeps the work slots and counters moving)
+        const int n = (t < NT && !(kPair && rank != 0)) ? w.nblk[t] : 0;
         qLo = qLo0 + (uint32_t)((qc % C::kQBufs) * (C::kTileBytes >> 4));
         const bool dual = (NT == 2) && !C::kTwoPos && w.nblk[0] > 0 && w.nblk[1] > 0;
         // The token covers the blocks both tiles have.  Past those (causal: tile 1 has one block more) the thread
@@ -899,10 +1018,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
           takeTurn();
           if (n > 0) {
-            issueQK(it, sKV + s0 * C::kTileBytes, 0);
-            issueQK(it, sKV + s0 * C::kTileBytes, 1);
-            ptx::tc_commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
-            if (n == 1) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
+            issueQK(it, sKV + s0 * C::kStageBytes, 0);
+            issueQK(it, sKV + s0 * C::kStageBytes, 1);
+            commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
+            if (n == 1) commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
           }
           passTurn();
           release(s0, n > 0);
@@ -938,21 +1057,21 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               wait_bar(bar(kBarKvFull + sK), phK, wc, 12);
               if constexpr (C::kRot) wait_bar(bar(kBarSFree + t), blk & 1, wc, 18);
               ptx::tc_fence_after();
-              issueQK(blk + 1, sKV + sK * C::kTileBytes, 0);
-              issueQK(blk + 1, sKV + sK * C::kTileBytes, 1);
-              ptx::tc_commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
-              if (j + 2 == n) ptx::tc_commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
+              issueQK(blk + 1, sKV + sK * C::kStageBytes, 0);
+              issueQK(blk + 1, sKV + sK * C::kStageBytes, 1);
+              commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
+              if (j + 2 == n) commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
             }
             if (j < n) {
               wait_bar(bar(kBarKvFull + sV), phV, wc, 10);
-              if (j == 0 && qc > 0) wait_bar(bar(kBarOFree + t), (qc - 1) & 1, wc, 19);
+              if (j == 0 && qc > 0) wait_bar(bar(kPair ? kBarOFreePair : kBarOFree + t), (qc - 1) & 1, wc, 19);
               wait_bar(bar(kBarP0Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 11);
               ptx::tc_fence_after();
-              issuePV(blk, sKV + sV * C::kTileBytes, j == 0 ? 0u : 1u, 0);
+              issuePV(blk, sKV + sV * C::kStageBytes, j == 0 ? 0u : 1u, 0);
               wait_bar(bar(kBarP1Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 15);
               ptx::tc_fence_after();
-              issuePV(blk, sKV + sV * C::kTileBytes, 1u, 1);
-              ptx::tc_commit(bar(kBarPvDone + 2 * t + (blk & 1)));
+              issuePV(blk, sKV + sV * C::kStageBytes, 1u, 1);
+              commit(bar(kBarPvDone + 2 * t + (blk & 1)));
             }
             if (hasNext) release(sK, j + 1 < n);
             release(sV, j < n);
@@ -1014,10 +1133,40 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // indices whose tile pair lies past the end of a short sequence (packed variable-length input) are
         // dropped here: nobody else hears of them
         int idx;
-        do {
-          idx = atomicAdd(p.workCounter, 1);
-          if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
-        } while (idx >= 0 && !make_work<NT, kVarlen>(p, idx, w));
+        if constexpr (kPair) {
+          // A work item is two neighbouring Q tiles (make_work with two tiles per item), one per CTA.  Rank 0 takes
+          // the index and hands it over through rank 1's shared memory (a mailbox per slot parity, full / empty
+          // barriers); both then work out the same description and keep their own tile of it as tile 0.
+          if (rank == 0) {
+            do {
+              idx = atomicAdd(p.workCounter, 1);
+              if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
+            } while (idx >= 0 && !make_work<2, kVarlen>(p, idx, w));
+            if (k >= 2) wait_bar(bar(kBarIdxEmpty + (k & 1)), ((k >> 1) - 1) & 1, wc, 26);
+            ptx::st_cluster_u32(ptx::mapa(ptx::smem_u32(&ctl->peerIdx[k & 1]), 1), (uint32_t)idx);
+            ptx::mbar_arrive_cluster_release(barBasePeer + 8u * (uint32_t)(kBarIdxFull + (k & 1)));
+          } else {
+            wait_bar_cluster(bar(kBarIdxFull + (k & 1)), (k >> 1) & 1, wc, 27);
+            idx = *reinterpret_cast<volatile int*>(&ctl->peerIdx[k & 1]);
+            if (*reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
+            ptx::mbar_arrive_cluster(barBasePeer + 8u * (uint32_t)(kBarIdxEmpty + (k & 1)));
+            if (idx >= 0) make_work<2, kVarlen>(p, idx, w);
+          }
+          if (idx >= 0) {
+            // Both tiles run every key block of the item in one M = 256 MMA.  A tile whose rows lie past the end of
+            // the sequence, or (causal) whose last block is entirely in the future, computes on zero-filled or fully
+            // masked scores and stores nothing for them.
+            w.qlo[0] = w.qlo[rank];
+            w.qhi[0] = w.qhi[rank];
+            w.nblk[0] = w.nmax;
+            w.nblk[1] = 0;
+          }
+        } else {
+          do {
+            idx = atomicAdd(p.workCounter, 1);
+            if (idx >= p.numWork || *reinterpret_cast<volatile int*>(&ctl->failed)) idx = -1;
+          } while (idx >= 0 && !make_work<NT, kVarlen>(p, idx, w));
+        }
         volatile WorkSlot* ws = &ctl->work[k & 1];
         ws->idx = idx;
         ws->sq = w.sq;
@@ -1052,12 +1201,21 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           // buffer qc % kQBufs was last used by item qc - kQBufs of this tile
           const int qb = qc[t] % C::kQBufs, qUse = qc[t] / C::kQBufs;  // buffer and how often it was used before
           if (qUse > 0) wait_bar(bar(kBarQEmpty + 2 * t + qb), (qUse - 1) & 1, wc, 22);
-          ptx::mbar_arrive_expect_tx(bar(kBarQFull + 2 * t + qb), C::kTileBytes);
           const uint32_t qDst = sQ + (t * C::kQBufs + qb) * C::kTileBytes;
+          if constexpr (kPair) {  // rank 0's barrier counts the Q tiles of both CTAs
+            if (rank == 0) ptx::mbar_arrive_expect_tx(bar(kBarQFull + 2 * t + qb), 2 * C::kTileBytes);
 #pragma unroll
-          for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_4d(qDst + a * kSubTileBytes, mapQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
-                             w.qRowTma + w.qlo[t], w.batchTma);
+            for (int a = 0; a < C::kSub; a++) {
+              ptx::tma_load_4d_pair(qDst + a * kSubTileBytes, mapQ, bar0(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
+                                    w.qRowTma + w.qlo[t], w.batchTma);
+            }
+          } else {
+            ptx::mbar_arrive_expect_tx(bar(kBarQFull + 2 * t + qb), C::kTileBytes);
+#pragma unroll
+            for (int a = 0; a < C::kSub; a++) {
+              ptx::tma_load_4d(qDst + a * kSubTileBytes, mapQ, bar(kBarQFull + 2 * t + qb), a * 64, w.unit * gp,
+                               w.qRowTma + w.qlo[t], w.batchTma);
+            }
           }
           qc[t]++;
         };
@@ -1074,7 +1232,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
           const int s = ld % NS;
           if (ld >= NS) wait_bar(bar(kBarKvEmpty + s), ((ld / NS) - 1) & 1, wc, 14);
-          ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
+          if constexpr (!kPair) ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
           bool isV;
           int blkIdx;
           if constexpr (C::kTwoPos) {  // K0 | K1 V0 | K2 V1 | ... | V(last)
@@ -1094,10 +1252,32 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
           const CUtensorMap* tm = isV ? mapV : mapK;
           const int row = w.kvRowTma + blkIdx * kBlockN;
+          if constexpr (kPair) {
+            // This CTA's half of the block, counted on rank 0's barrier together with the other half.
+            // K: keys [64 rank, 64 rank + 64), all of the head dim (the K map's box is 64 rows high);
+            // V: all 128 keys, two 64-wide slabs of the head dim (v_slab_offset).
+            const uint32_t dst = sKV + s * C::kStageBytes;
+            if (isV) {
+              if (rank == 0) ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), 2 * 2 * kSubTileBytes);
 #pragma unroll
-          for (int a = 0; a < C::kSub; a++) {
-            ptx::tma_load_4d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row,
-                             w.batchTma);
+              for (int a = 0; a < 2; a++) {
+                ptx::tma_load_4d_pair(dst + a * kSubTileBytes, tm, bar0(kBarKvFull + s), v_slab_offset<HDP>((int)rank, a), w.hkv,
+                                      row, w.batchTma);
+              }
+            } else {
+              if (rank == 0) ptx::mbar_arrive_expect_tx(bar(kBarKvFull + s), C::kTileBytes);
+#pragma unroll
+              for (int a = 0; a < C::kSub; a++) {
+                ptx::tma_load_4d_pair(dst + a * (kSubTileBytes / 2), tm, bar0(kBarKvFull + s), a * 64, w.hkv,
+                                      row + (int)rank * (kBlockN / 2), w.batchTma);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int a = 0; a < C::kSub; a++) {
+              ptx::tma_load_4d(sKV + s * C::kTileBytes + a * kSubTileBytes, tm, bar(kBarKvFull + s), a * 64, w.hkv, row,
+                               w.batchTma);
+            }
           }
           // the stage-free arrival of every tile that will not touch this block
 #pragma unroll
@@ -1122,15 +1302,23 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // stream and per captured launch precisely to rule that out): report it rather than return a result with rows
       // that nobody computed.
       const int taken = *reinterpret_cast<volatile int*>(p.workCounter);
-      if (taken != p.numWork + (int)gridDim.x && *wc.failed == 0) atomicExch(p.status, (p.epoch << 8) | 30);
+      const int takers = kPair ? (int)gridDim.x / 2 : (int)gridDim.x;  // pair form: rank 0 of each pair takes indices
+      if (taken != p.numWork + takers && *wc.failed == 0) atomicExch(p.status, (p.epoch << 8) | 30);
       p.workCounter[0] = 0;
       p.workCounter[1] = 0;
     }
   }
+  // pair form: neither CTA leaves (or frees tensor memory) while the other may still reach into its shared memory
+  // or have MMAs of the pair in flight
+  if constexpr (kPair) ptx::cluster_sync();
   if (warp == kIssueWarpA) {
     if (*wc.failed) __nanosleep(200000);  // a wait gave up: let whatever is still in flight drain before freeing
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem, C::kTmemCols);
+    if constexpr (kPair) {
+      ptx::tmem_dealloc_pair(tmem, C::kTmemCols);
+    } else {
+      ptx::tmem_dealloc(tmem, C::kTmemCols);
+    }
   }
 }
 

@@ -34,6 +34,7 @@ int device_num_sms(int device);       // c_abi.cu
 int option_narrow_mma();              // c_abi.cu: MMAs shaped for head dims 32 / 96 inside the 64- / 128-wide kernels
 int option_solo64();                  // c_abi.cu: one-tile CTAs, two per SM, for head dims 32 / 64
 int option_work_order();              // c_abi.cu: -1 auto, 0 pair index fastest, n > 0 chunk width
+int option_pair_cta();                // c_abi.cu: head dims 192 / 256 in clusters of two CTAs that share K/V
 
 #define TFA_CAT3(a, b, c) a##b##c
 #define TFA_NAME(hdp, bf) TFA_CAT3(launch_fwd_tc_hdp##hdp, _bf, bf)
@@ -96,6 +97,22 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   }
 #endif
 
+  bool pair = false;  // clusters of two CTAs, one Q tile each, K/V shared (head dims 192 / 256, fixed length)
+#if TFA_HDP >= 192
+  // Measured (fp16, B8 H16, 800-launch loops): head dim 256 non-causal S2048 872 -> 1125, S8192 957 -> 1244, causal S2048
+  // 757 -> 834 TFLOP/s; head dim 192 non-causal 933 -> 984 (S2048), 1041 -> 1088 (S8192), causal 787 -> 751.  Causal
+  // pairs pay for the fully masked last block of their first tile and, with short sequences, for item boundaries that
+  // are twice as heavy; "auto" therefore leaves causal head dim 192 and short causal head dim 256 to the one-tile form.
+  const int pairOpt = option_pair_cta();
+  const bool pairAuto = (TFA_HDP == 256) ? (!pr.causal || pr.seqLenQ >= 2048) : !pr.causal;
+  pair = !varlen && pr.seqLenQ > (tc::kBlockM >> packShift) && (pairOpt > 0 || (pairOpt < 0 && pairAuto));
+  if (pair) {
+    kernel = tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed, false, TFA_HDP, true>;
+    kNT = 2;  // a work item is the two tiles of a pair
+    smemBytes = tc::CfgPair<TFA_HDP>::kSmemBytes;
+  }
+#endif
+
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return kCudaError;
   static std::once_flag once[64];
@@ -109,6 +126,12 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
     attrErr[device] = cudaSuccess;
     bigAttr(tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed>);
     bigAttr(tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeVarlen>);
+#if TFA_HDP >= 192
+    if (attrErr[device] == cudaSuccess) {
+      attrErr[device] = cudaFuncSetAttribute(tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed, false, TFA_HDP, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, tc::CfgPair<TFA_HDP>::kSmemBytes);
+    }
+#endif
 #if TFA_HDP == 128
     bigAttr(tc::fwd_tc_kernel<128, kBf, tc::kModeFixed, false, 96>);
     bigAttr(tc::fwd_tc_kernel<128, kBf, tc::kModeVarlen, false, 96>);
@@ -146,7 +169,8 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   const long long rowsQ = varlen ? (devMaps ? 1 : pr.totalQ) : pr.seqLenQ;
   const long long rowsKV = varlen ? (devMaps ? 1 : pr.totalKV) : pr.seqLenKV;
   if ((rc = make_map(&tmQ, pr.Q, nb, rowsQ, pr.headsQ, pr.headDim, gp, rowsPerTile)) != kOk) return rc;
-  if ((rc = make_map(&tmK, pr.K, nb, rowsKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
+  // pair form: each CTA loads 64 of a block's 128 keys
+  if ((rc = make_map(&tmK, pr.K, nb, rowsKV, pr.headsKV, pr.headDim, 1, pair ? tc::kBlockN / 2 : tc::kBlockN)) != kOk) return rc;
   if ((rc = make_map(&tmV, pr.V, nb, rowsKV, pr.headsKV, pr.headDim, 1, tc::kBlockN)) != kOk) return rc;
 
   TcParams p;
@@ -209,8 +233,37 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
   // persistent: one CTA per SM (512 tensor-memory columns and ~200 KB of shared memory each), or two of the small form
   const long long slots = (long long)device_num_sms(device) * (solo ? 2 : 1);
   const int ctas = (int)(numWork < slots ? numWork : slots);
-  kernel<<<dim3((unsigned)ctas), threads, smemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (pair) {
+    // one cluster of two CTAs per work item in flight; as many clusters as the device runs at once
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = (size_t)smemBytes;
+    cfg.stream = pr.stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int maxClusters[64] = {0};
+    if (maxClusters[device] == 0) {
+      cfg.gridDim = dim3((unsigned)(2 * (device_num_sms(device) / 2)));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        n = device_num_sms(device) / 2;
+      }
+      maxClusters[device] = n;
+    }
+    const long long clusters = numWork < maxClusters[device] ? numWork : maxClusters[device];
+    cfg.gridDim = dim3((unsigned)(2 * clusters));
+    e = cudaLaunchKernelEx(&cfg, kernel, tmQ, tmK, tmV, p);
+  } else {
+    kernel<<<dim3((unsigned)ctas), threads, smemBytes, pr.stream>>>(tmQ, tmK, tmV, p);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) {
     set_error_string("kernel launch failed: %s", cudaGetErrorString(e));
     return kCudaError;

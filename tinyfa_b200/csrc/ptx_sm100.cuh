@@ -106,6 +106,61 @@ __device__ __forceinline__ void tensormap_acquire(const void* globalMap) {
   asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(globalMap) : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cluster of two)
+// The kernels that run one tcgen05.mma over two SMs launch clusters of two CTAs.  Rank 0 issues the MMAs; barriers
+// that it waits on are reached from the other CTA through the cluster window of the shared address space.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t localAddr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(localAddr), "r"(rank));
+  return a;
+}
+// Arrival on a barrier of either CTA of the pair.  Plain form: it hands over no generic-proxy data (what it orders -
+// tensor-memory stores against the other CTA's MMAs - is covered by the tcgen05 fences around it); a cluster-scope
+// release here was measured at ~1000 clocks per arrival in the softmax loop.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// Arrival that publishes this thread's earlier stores into the other CTA's shared memory (pairs with mbar_try_wait_cluster).
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// wait that also makes the other CTA's plain stores (made before its cluster-scope arrival) visible
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t clusterAddr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(clusterAddr), "r"(v) : "memory");
+}
+// all threads of both CTAs
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 4-D tiled load into this CTA's shared memory whose completion bytes are counted on a barrier that may live in
+// the other CTA of the pair (clusterBar: a shared::cluster address).  No broadcast: every CTA loads its own data.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smemDst, const void* desc, uint32_t clusterBar, int x, int y, int z,
+                                                 int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smemDst), "l"(desc), "r"(clusterBar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- register reallocation
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
@@ -130,6 +185,18 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t nCols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(nCols) : "memory");
 }
 
+// CTA-pair forms: one warp of each CTA of the pair executes them, with the same shared-memory offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smemDst, uint32_t nCols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemDst), "r"(nCols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t nCols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(nCols) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -150,6 +217,14 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // mbarrier arrives once every tcgen05.mma previously issued by this thread has completed.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// CTA-pair form (the two CTAs of a cluster of two issue one MMA over both SMs): the arrival is delivered to the
+// barrier at the same shared-memory offset in every CTA of ctaMask.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t ctaMask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(ctaMask)
+               : "memory");
 }
 
 // D[tmem] (+)= A * B, 16-bit inputs, fp32 accumulate, one thread issues; A from shared memory (mma_ss_lohi) or from
@@ -178,6 +253,36 @@ __device__ __forceinline__ void mma_ts_lohi(uint32_t dTmem, uint32_t aTmem, uint
       "mov.b64 db, {%2, %3};\n\t"
       "setp.ne.b32 p, %5, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n" ::"r"(dTmem),
+      "r"(aTmem), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate)
+      : "memory");
+}
+
+// CTA-pair forms (M = 256: rows 0-127 are this CTA's, 128-255 the other's; each CTA supplies its 128 rows of A and
+// half of B's N columns from the same shared-memory offsets, and receives its 128 rows of D in its own tensor memory).
+__device__ __forceinline__ void mma_ss_lohi_pair(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
+                                                 uint32_t iDesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n" ::"r"(dTmem),
+      "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lohi_pair(uint32_t dTmem, uint32_t aTmem, uint32_t bLo, uint32_t bHi, uint32_t iDesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n\t"
       "}\n" ::"r"(dTmem),
       "r"(aTmem), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate)
       : "memory");
