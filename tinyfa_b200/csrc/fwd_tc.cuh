@@ -163,7 +163,7 @@ struct CfgPair {
   static constexpr int kNT = 1;
   static constexpr int kQBufs = 1;
   static constexpr int kStageBytes = 2 * kSubTileBytes;  // K: 64 keys x HDP (<= 32 KB); V: 128 keys x two 64-wide slabs
-  static constexpr int kStages = (HDP == 256) ? 4 : 5;
+  static constexpr int kStages = (HDP == 256) ? 4 : 5;  // a fifth stage at 256 (exactly the 227 KB limit) measured no different
   static constexpr int kTmemCols = 512;
   static constexpr bool kRot = false;
   static constexpr bool kDblS = true;
@@ -520,6 +520,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   constexpr int NS = C::kStages;
   constexpr bool kVarlen = (kMode == kModeVarlen);
   static_assert(NS <= 6, "barrier slots");
+  // One-tile forms: a ring stage's "free" barrier completes exactly when the MMAs that read the stage have finished,
+  // i.e. when S of that K block (resp. O += P.V of that V block) is ready, and one issuing thread feeds the tensor
+  // pipe, which idles while that thread executes a tcgen05.commit (~120-150 clocks each).  So the softmax and output
+  // warps wait on the ring barriers themselves (they can work out every block's ring position from the running load
+  // count) and the issuing thread commits twice per block instead of four times.  With two tiles per CTA a stage is
+  // free only when both tiles are done with it, which says nothing about one tile's S, so they keep their own barriers.
+  // Not with a ring of two stages (head dim 256, one-tile form): there K of block j + 1 re-uses the stage of K of block
+  // j and its Q.K^T is issued before P.V of block j, so the stage's barrier could complete a second time before a slow
+  // softmax warp has looked at it once, and a parity wait cannot tell the two apart.  From three stages on, whatever
+  // re-uses a stage is consumed at or after P.V of the block whose scores the waiting warp is about to produce.
+  constexpr bool kRingSig = (NT == 1 && NS >= 3);
+  static_assert(!kRingSig || C::kTwoPos, "one-tile forms alternate S between two positions");
 
   extern __shared__ uint8_t smemRaw[];
   const uint32_t rawAddr = ptx::smem_u32(smemRaw);
@@ -647,14 +659,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (idx < 0 || *wc.failed) break;
       if (w.nmax == 0) continue;
       const int ldItem = ldBase;
-      if constexpr (kVarlen) ldBase += 2 * w.nmax;
+      if constexpr (kVarlen || kRingSig) ldBase += 2 * w.nmax;
       (void)ldItem;
       if (t >= NT || w.nblk[t] == 0) continue;
       const int qpos = w.qlo[t] + (r >> p.packShift);
       float m = -INFINITY, l = 0.f;
       const int n = w.nblk[t];
       for (int j = 0; j < n; j++, it++) {
-        wait_bar(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)), (C::kTwoPos ? (it >> 1) : it) & 1, wc, 1);
+        if constexpr (kRingSig) {  // ring order K0 | K1 V0 | K2 V1 | ...: K of block j is load 2 j - 1 of the item (K0: 0)
+          const int g = ldItem + (j == 0 ? 0 : 2 * j - 1);
+          wait_bar(bar(kBarKvEmpty + g % NS), (g / NS) & 1, wc, 1);
+        } else {
+          wait_bar(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)), (C::kTwoPos ? (it >> 1) : it) & 1, wc, 1);
+        }
         ptx::tc_fence_after();
         uint32_t v[4][32];
         const uint32_t tS = tRegion + (uint32_t)((it & 1) * C::kSPosStride);   // S of this block
@@ -726,8 +743,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           // phase in progress or the one just completed: P.V of block it-2 finished before S of this block was
           // produced, and P.V of this block cannot start before this warp arrives.)
           const float scale = grow ? ex2((m - mNew) * c) : 1.f;
-          wait_bar(bar(kBarPvDone + 2 * t + (C::kTwoPos ? ((it - 1) & 1) : 0)),
-                   (C::kTwoPos ? ((it - 1) >> 1) : (it - 1)) & 1, wc, 5);
+          if constexpr (kRingSig) {  // V of block j - 1 is load 2 j of the item (j >= 1 here: block 0 never rescales)
+            const int g = ldItem + 2 * j;
+            wait_bar(bar(kBarKvEmpty + g % NS), (g / NS) & 1, wc, 5);
+          } else {
+            wait_bar(bar(kBarPvDone + 2 * t + (C::kTwoPos ? ((it - 1) & 1) : 0)),
+                     (C::kTwoPos ? ((it - 1) >> 1) : (it - 1)) & 1, wc, 5);
+          }
           ptx::tc_fence_after();
           const uint32_t tO = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::kOCol0 + t * HDP);
 #pragma unroll 1
@@ -791,8 +813,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if constexpr (kSolo) {
         // This warp is also the epilogue of its 32 rows: wait for the last P.V of the item, read O, release the
         // accumulator to the next item, normalise, convert and store.  Meanwhile the SM's other CTA keeps computing.
-        const int lastBlk = it - 1;
-        wait_bar(bar(kBarPvDone + 2 * t + (lastBlk & 1)), (lastBlk >> 1) & 1, wc, 7);
+        const int gLast = ldItem + 2 * w.nmax - 1;  // the item's last load is V of its last block
+        wait_bar(bar(kBarKvEmpty + gLast % NS), (gLast / NS) & 1, wc, 7);
         ptx::tc_fence_after();
         const float inv = (l > 0.f) ? (1.f / l) : 0.f;
         const int gp = 1 << p.packShift;
@@ -842,6 +864,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int gp = 1 << p.packShift;
     int items[2] = {0, 0};    // work items in which tile t was active
     int pvTotal[2] = {0, 0};  // blocks of tile t issued so far
+    int ldBase = 0;           // K/V ring loads of all earlier items
     for (int k = 0;; k++) {
       Work w;
       const int idx = fetchWork(k, w);
@@ -849,6 +872,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
       if (idx < 0 || *wc.failed) break;
       if (w.nmax == 0) continue;
+      const int gLast = ldBase + 2 * w.nmax - 1;  // the item's last load: V of its last block
+      ldBase += 2 * w.nmax;
+      (void)gLast;
 #pragma unroll
       for (int t = 0; t < NT; t++) {
         const int n = w.nblk[t];
@@ -860,7 +886,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // last P, i.e. after all earlier P.V of the tile, and the next item's P.V waits for kBarOFree below.
         // (with two S positions P.V of block X-1 may still be running at this point: its barrier is the other one)
         const int lastBlk = pvTotal[t] - 1;
-        wait_bar(bar(kBarPvDone + 2 * t + (C::kTwoPos ? (lastBlk & 1) : 0)), (C::kTwoPos ? (lastBlk >> 1) : lastBlk) & 1, wc, 7);
+        if constexpr (kRingSig) {
+          wait_bar(bar(kBarKvEmpty + gLast % NS), (gLast / NS) & 1, wc, 7);
+        } else {
+          wait_bar(bar(kBarPvDone + 2 * t + (C::kTwoPos ? (lastBlk & 1) : 0)), (C::kTwoPos ? (lastBlk >> 1) : lastBlk) & 1, wc, 7);
+        }
         ptx::tc_fence_after();
         const float inv = (l > 0.f) ? (1.f / l) : 0.f;
         const int qpos = w.qlo[t] + (r >> p.packShift);
@@ -1020,11 +1050,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (n > 0) {
             issueQK(it, sKV + s0 * C::kStageBytes, 0);
             issueQK(it, sKV + s0 * C::kStageBytes, 1);
-            commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
+            if constexpr (kRingSig) {
+              release(s0, true);  // doubles as "S of block 0 is ready"
+            } else {
+              commit(bar(kBarSFull + 2 * t + (C::kTwoPos ? (it & 1) : 0)));
+            }
             if (n == 1) commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));  // Q tile no longer needed
           }
           passTurn();
-          release(s0, n > 0);
+          if constexpr (!kRingSig) release(s0, n > 0);
           ld++;
         }
         for (int j = 0; j < w.nmax; j++) {
@@ -1059,7 +1093,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               ptx::tc_fence_after();
               issueQK(blk + 1, sKV + sK * C::kStageBytes, 0);
               issueQK(blk + 1, sKV + sK * C::kStageBytes, 1);
-              commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
+              if constexpr (kRingSig) {
+                release(sK, true);  // the stage is free when these MMAs finish, which is when S of block j + 1 is ready
+              } else {
+                commit(bar(kBarSFull + 2 * t + ((blk + 1) & 1)));
+              }
               if (j + 2 == n) commit(bar(kBarQEmpty + 2 * t + (qc % C::kQBufs)));
             }
             if (j < n) {
@@ -1071,10 +1109,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               wait_bar(bar(kBarP1Ready + 2 * t + (blk & 1)), (blk >> 1) & 1, wc, 15);
               ptx::tc_fence_after();
               issuePV(blk, sKV + sV * C::kStageBytes, 1u, 1);
-              commit(bar(kBarPvDone + 2 * t + (blk & 1)));
+              if constexpr (kRingSig) {
+                release(sV, true);  // ... and likewise "O += P.V of block j has finished"
+              } else {
+                commit(bar(kBarPvDone + 2 * t + (blk & 1)));
+              }
             }
-            if (hasNext) release(sK, j + 1 < n);
-            release(sV, j < n);
+            if constexpr (!kRingSig) {
+              if (hasNext) release(sK, j + 1 < n);
+              release(sV, j < n);
+            }
             continue;
           }
           bool p1Ready = false;

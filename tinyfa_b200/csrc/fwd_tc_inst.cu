@@ -99,12 +99,13 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
 
   bool pair = false;  // clusters of two CTAs, one Q tile each, K/V shared (head dims 192 / 256, fixed length)
 #if TFA_HDP >= 192
-  // Measured (fp16, B8 H16, 800-launch loops): head dim 256 non-causal S2048 872 -> 1125, S8192 957 -> 1244, causal S2048
-  // 757 -> 834 TFLOP/s; head dim 192 non-causal 933 -> 984 (S2048), 1041 -> 1088 (S8192), causal 787 -> 751.  Causal
-  // pairs pay for the fully masked last block of their first tile and, with short sequences, for item boundaries that
-  // are twice as heavy; "auto" therefore leaves causal head dim 192 and short causal head dim 256 to the one-tile form.
+  // Measured (fp16, B8 H16, 800-launch loops, one-tile form -> pair form): head dim 256 non-causal S2048 872 -> 1168,
+  // S8192 957 -> 1244, causal S2048 760 -> 859 TFLOP/s; head dim 192 non-causal 1023 -> 1013, causal 826 -> 764 (three
+  // ring stages already keep its one-tile form fed).  Causal pairs pay for the fully masked last block of their first
+  // tile and, with short sequences, for item boundaries that are twice as heavy; "auto" is head dim 256 only, and its
+  // causal problems from 2048 query rows.
   const int pairOpt = option_pair_cta();
-  const bool pairAuto = (TFA_HDP == 256) ? (!pr.causal || pr.seqLenQ >= 2048) : !pr.causal;
+  const bool pairAuto = (TFA_HDP == 256) && (!pr.causal || pr.seqLenQ >= 2048);
   pair = !varlen && pr.seqLenQ > (tc::kBlockM >> packShift) && (pairOpt > 0 || (pairOpt < 0 && pairAuto));
   if (pair) {
     kernel = tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed, false, TFA_HDP, true>;
