@@ -213,7 +213,9 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
     long long heads = (32ll << 20) / (kvPerHead > 0 ? kvPerHead : 1);
     if (heads < 1) heads = 1;
     long long width = heads * unitsPerKvHead;
-    const long long minWidth = (2ll * device_num_sms(device) + p.numPairs - 1) / p.numPairs;
+    // two items per worker: a worker is a CTA, or in the pair form a cluster of two
+    const long long workers = pair ? device_num_sms(device) / 2 : device_num_sms(device);
+    const long long minWidth = (2ll * workers + p.numPairs - 1) / p.numPairs;
     if (width < minWidth) width = minWidth;
     const long long per = (long long)p.numUnits * pr.batch;
     if (width > per) width = per;
