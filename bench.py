@@ -65,6 +65,8 @@ WORKLOADS = {
     "fp16_causal_b8_s2048_h16_d96": _fixed("fp16", True, 8, 2048, 2048, 16, 16, 96),
     "fp16_causal_b8_s2048_h16_d192": _fixed("fp16", True, 8, 2048, 2048, 16, 16, 192),
     "fp16_causal_b8_s2048_h16_d256": _fixed("fp16", True, 8, 2048, 2048, 16, 16, 256),
+    # the same sizes without the mask: the CTA-pair form of head dim 256 with every key block a full one
+    "fp16_noncausal_b8_s2048_h16_d256": _fixed("fp16", False, 8, 2048, 2048, 16, 16, 256),
     # fp32 runs on the CUDA cores (no TF32): the small known-answer shape and a throughput shape
     "fp32_noncausal_b1_s128_h4_d64": _fixed("fp32", False, 1, 128, 128, 4, 4, 64),
     "fp32_noncausal_b2_s4096_h32_d128": _fixed("fp32", False, 2, 4096, 4096, 32, 32, 128),
@@ -82,11 +84,11 @@ NCU_TRAFFIC_BYTES = {
     "bf16_causal_b2_s4096_h32_d128": 266387456,
     "bf16_causal_varlen_gqa_16seq_h32_8_d128": 1343037184,
     "bf16_causal_gqa_b4_s8192_h32_8_d128": 644488192,
-    "fp16_causal_b8_s2048_h16_d64": 115396096,
-    "fp16_causal_b8_s2048_h16_d32": 53254912,
+    "fp16_causal_b8_s2048_h16_d64": 114779392,
+    "fp16_causal_b8_s2048_h16_d32": 52913664,
     "fp16_causal_b8_s2048_h16_d96": 184531200,
-    "fp16_causal_b8_s2048_h16_d192": 384580864,
-    "fp16_causal_b8_s2048_h16_d256": 523113216,
+    "fp16_causal_b8_s2048_h16_d192": 386672128,
+    "fp16_causal_b8_s2048_h16_d256": 524141824,
     "fp32_noncausal_b2_s4096_h32_d128": 518427392,
     "bf16_decode_b8_skv32768_h32_8_d128": 1078060032,
     "bf16_decode_b64_skv32768_h32_8_d128": 8624480256,

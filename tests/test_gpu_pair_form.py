@@ -93,3 +93,49 @@ def test_pair_form_leaves_rows_past_the_output_alone_and_reports_no_timeout():
         tf.set_option("pair_cta", -1)
     assert (buf[Sq * 2 * D:] == 7.0).all()
     tf.device_status()
+
+
+def test_pair_form_on_many_streams_and_in_a_replayed_graph():
+    """Cluster launches take their work counters like every other launch: per stream, or per captured launch.  Forty
+    streams with pair-form launches in flight and a captured pair-form launch replayed in between all give the bits
+    of a launch that ran alone."""
+    lib = tf._lib.load()
+    B, Sq, Skv, Hq, Hkv, D = 1, 640, 640, 6, 6, 256
+    g = torch.Generator(device="cuda").manual_seed(5)
+    Q = torch.randn(B, Sq, Hq, D, generator=g, device="cuda").to(torch.bfloat16)
+    K = torch.randn(B, Skv, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+    V = torch.randn(B, Skv, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+
+    def launch(O, stream):
+        return lib.tfa_b200_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), 2, B, Sq, Skv, Hq, Hkv, D, 1, stream)
+
+    try:
+        tf.set_option("pair_cta", 1)
+        alone = torch.zeros_like(Q)
+        assert launch(alone, torch.cuda.current_stream().cuda_stream) == 0, tf._lib.last_error()
+        torch.cuda.synchronize()
+        Og = torch.zeros_like(Q)
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                rc = launch(Og, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, tf._lib.last_error()
+        streams = [torch.cuda.Stream() for _ in range(40)]
+        outs = [torch.zeros_like(Q) for _ in range(80)]
+        torch.cuda.synchronize()
+        replay_stream = torch.cuda.Stream()
+        for rep in range(2):
+            for i, st in enumerate(streams):
+                assert launch(outs[rep * 40 + i], st.cuda_stream) == 0, tf._lib.last_error()
+                if i % 10 == 0:
+                    with torch.cuda.stream(replay_stream):
+                        graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        tf.set_option("pair_cta", -1)
+    assert torch.equal(Og, alone)
+    for O in outs:
+        assert torch.equal(O, alone)
+    tf.device_status()

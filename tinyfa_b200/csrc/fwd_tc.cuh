@@ -23,6 +23,10 @@
 //   [t*128, t*128+128)            S of Q tile t; the 16-bit P overwrites the first 64 columns
 //   [256 + t*HDP, 256+(t+1)*HDP)  O of Q tile t (NT == 2, HDP == 128), or [128, 128+HDP) when NT == 1
 //   HDP == 64: 192 columns per tile with S alternating between two positions (see Cfg::kRot), O at 384 + t*64
+//
+// Three CTA forms share this kernel body: two Q tiles per CTA and one CTA per SM (HDP 128; HDP 192 / 256 with one tile),
+// one tile per CTA and two CTAs per SM (CfgSolo64, head dims 32 / 64), and clusters of two one-tile CTAs that share
+// every K/V block through tcgen05.mma.cta_group::2 (CfgPair, head dims 192 / 256).
 #pragma once
 
 #include <cuda.h>
