@@ -92,7 +92,7 @@ int tfa_b200_device_status(int* site);
  *   "solo64" 0/1       head dims 32 / 64: two-tile CTAs, one per SM / one-tile CTAs, two per SM (the default)
  *   "pair_cta" -1/0/1  head dims 192 / 256, fixed-length input: clusters of two CTAs that work on two neighbouring query
  *                      tiles and share every K/V block through one MMA over both SMs (tcgen05 cta_group::2):
- *                      auto (head dim 256: non-causal, and causal from 2048 query rows; head dim 192: never, its
+ *                      auto (head dim 256: non-causal, and causal from 1024 query rows; head dim 192: never, its
  *                      one-tile form measures as fast) / never / wherever it applies.  Results are bit-identical to
  *                      the one-tile form.
  *   "work_order" -1/0/n  order in which the persistent kernel hands out (query tile pair, head, batch) items:

@@ -411,23 +411,25 @@ struct Work {
 };
 
 // Packed variable-length input, last key block of a sequence: overwrite the rows of the V tile that lie past the end
-// of the sequence with zeros (one thread per key row), once the tile has landed.  Kept out of line: it runs once per
-// sequence and tile, and inlined into the softmax loop it slows every other block down.
+// of the sequence with zeros (they are the next sequence's, and P = 0 times a NaN or Inf stored there would still
+// poison O; the reference zero-fills rows past a sequence end, reference csrc/flash_attn/mma/memory.cuh:52-59).  One
+// warp, four key rows per lane, once the tile has landed.  K needs nothing: its columns are masked whatever they hold.
 template <int kSub>
-__device__ __noinline__ void zero_v_tail(uint32_t kvFullBar, uint32_t phase, const WaitCtx wc, uint32_t tileAddr, int row,
-                                         int tail) {
-  wait_bar(kvFullBar, phase, wc, 25);
-  if (row >= tail) {  // key rows [tail, 128) of the block are not this sequence's
-    const uint32_t rowAddr = tileAddr + (uint32_t)(row * 128);
+__device__ __forceinline__ void zero_v_tail(uint32_t tileAddr, int lane, int tail) {
+  for (int row = lane; row < kBlockN; row += 32) {
+    if (row >= tail) {  // key rows [tail, 128) of the block are not this sequence's
+      const uint32_t rowAddr = tileAddr + (uint32_t)(row * 128);
 #pragma unroll
-    for (int a = 0; a < kSub; a++) {
+      for (int a = 0; a < kSub; a++) {
 #pragma unroll
-      for (int q = 0; q < 8; q++) {
-        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowAddr + a * kSubTileBytes + q * 16), "r"(0u) : "memory");
+        for (int q = 0; q < 8; q++) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(rowAddr + a * kSubTileBytes + q * 16), "r"(0u) : "memory");
+        }
       }
     }
   }
   ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+  __syncwarp();
 }
 
 // Work item idx -> (query tile pair, Q head unit, batch entry).  Two orders.  Pair index fastest: CTAs running at the
@@ -520,9 +522,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   constexpr int kSoftmaxWarps = kSolo ? 4 : 8;
   constexpr int kEpilogueEnd = kSolo ? 4 : 12;  // epilogue warps are [kSoftmaxWarps, kEpilogueEnd): none in the solo form
   constexpr int kIssueWarpA = kSolo ? 4 : 12, kIssueWarpB = kSolo ? -1 : kIssuerB, kLoadWarp = kSolo ? 5 : 13;
-  constexpr int kConsumers = kSolo ? 5 : kWorkConsumers;  // roles that read every work item
-  constexpr int NS = C::kStages;
   constexpr bool kVarlen = (kMode == kModeVarlen);
+  // Packed input has one more role: a warp that is idle otherwise (14, or 6 in the one-tile form) zeroes the V rows
+  // past a sequence's end and takes part in every "first half of P ready" barrier, so that no P.V can start before
+  // the rows are clean.  Kept out of the softmax warps: the same code inside their block loop, executed once per
+  // sequence and tile, cost the packed kernel 4-5 % on every block.
+  constexpr int kHelpWarp = kSolo ? 6 : 14;
+  constexpr int kConsumers = (kSolo ? 5 : kWorkConsumers) + (kVarlen ? 1 : 0);  // roles that read every work item
+  constexpr int NS = C::kStages;
   static_assert(NS <= 6, "barrier slots");
   // One-tile forms: a ring stage's "free" barrier completes exactly when the MMAs that read the stage have finished,
   // i.e. when S of that K block (resp. O += P.V of that V block) is ready, and one issuing thread feeds the tensor
@@ -565,7 +572,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int u = 0; u < 2; u++) {
         ptx::mbar_init(bar(kBarQFull + 2 * t + u), 1);
         ptx::mbar_init(bar(kBarQEmpty + 2 * t + u), 1);
-        ptx::mbar_init(bar(kBarP0Ready + 2 * t + u), kPair ? 8 : 4);  // pair form: the softmax warps of both CTAs
+        // pair form: the softmax warps of both CTAs; packed input: the four softmax warps and the V-tail warp
+        ptx::mbar_init(bar(kBarP0Ready + 2 * t + u), kPair ? 8 : (kVarlen ? 5 : 4));
         ptx::mbar_init(bar(kBarP1Ready + 2 * t + u), kPair ? 8 : 4);
         ptx::mbar_init(bar(kBarSFull + 2 * t + u), 1);
         ptx::mbar_init(bar(kBarPvDone + 2 * t + u), 1);
@@ -663,7 +671,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (idx < 0 || *wc.failed) break;
       if (w.nmax == 0) continue;
       const int ldItem = ldBase;
-      if constexpr (kVarlen || kRingSig) ldBase += 2 * w.nmax;
+      if constexpr (kRingSig) ldBase += 2 * w.nmax;
       (void)ldItem;
       if (t >= NT || w.nblk[t] == 0) continue;
       const int qpos = w.qlo[t] + (r >> p.packShift);
@@ -785,19 +793,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           } else {
             expQuarter(v[2], negMc, pkA, sum2, 2);
             expQuarter(v[3], negMc, pkB, sum2, 3);
-          }
-          if constexpr (kVarlen) {
-           if (half == 0 && kbase + kBlockN > w.skv) {
-            // Packed variable-length input: the rows of this V block past the end of the sequence are the next
-            // sequence's, and P = 0 times a NaN or Inf stored there would still poison O.  The reference zero-fills
-            // rows past a sequence end (reference csrc/flash_attn/mma/memory.cuh:52-59); here the softmax warps
-            // overwrite them with zeros in shared memory before they let P.V of this block start.  (Both tiles do
-            // it, each ahead of its own P.V; K needs nothing, its columns are masked whatever they hold.)
-            const int vi = C::kTwoPos ? ((j == w.nmax - 1) ? 2 * w.nmax - 1 : 2 * j + 2) : 2 * j + 1;  // ring order
-            const int ldv = ldItem + vi;
-            zero_v_tail<C::kSub>(bar(kBarKvFull + ldv % NS), (ldv / NS) & 1, wc,
-                                 sKV + (uint32_t)((ldv % NS) * C::kTileBytes), r, w.skv - kbase);
-           }
           }
           ptx::tmem_st_32x32b_x16(tP + half * 32, pkA);
           ptx::tmem_st_32x32b_x16(tP + half * 32 + 16, pkB);
@@ -1334,6 +1329,52 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
         if (!nextDone) more = publish(k + 1);
+      }
+    } else if (kVarlen && warp == kHelpWarp) {
+      // ============================================================== packed input: V rows past a sequence's end
+      int ldBase = 0;         // K/V ring loads of all earlier items
+      int cnt[2] = {0, 0};    // blocks of tile t so far, over all items (phase of its P-ready barriers)
+      for (int k = 0;; k++) {
+        Work w;
+        const int idx = fetchWork(k, w);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(kBarWorkEmpty + (k & 1)));
+        if (idx < 0 || *wc.failed) break;
+        if (w.nmax == 0) continue;
+        const int ldv = ldBase + 2 * w.nmax - 1;  // the item's last load is V of its last block
+        ldBase += 2 * w.nmax;
+        const int nTotal = (w.skv + kBlockN - 1) / kBlockN;
+        const int tail = w.skv - (nTotal - 1) * kBlockN;  // keys of the sequence in its last block
+        for (int j = 0; j < w.nmax; j++) {
+          if (j == nTotal - 1 && tail < kBlockN) {  // some tile of this item reaches the ragged last block
+            // First wait until the scores of this block exist for a tile that has it: K of the block has then been
+            // consumed, so the ring is at most one use of V's stage behind and the parity wait below asks for the phase
+            // in progress or the one just completed.  (Straight after the previous block's barrier the ring may be two
+            // uses behind, and a parity wait for a phase two ahead returns at once.)
+            const int tz = (j < w.nblk[0]) ? 0 : 1;
+            if constexpr (kRingSig) {
+              const int g = (ldv - (2 * w.nmax - 1)) + (j == 0 ? 0 : 2 * j - 1);
+              wait_bar(bar(kBarKvEmpty + g % NS), (g / NS) & 1, wc, 24);
+            } else {
+              wait_bar(bar(kBarSFull + 2 * tz + (C::kTwoPos ? (cnt[tz] & 1) : 0)), (C::kTwoPos ? (cnt[tz] >> 1) : cnt[tz]) & 1, wc, 24);
+            }
+            wait_bar(bar(kBarKvFull + ldv % NS), (ldv / NS) & 1, wc, 25);
+            zero_v_tail<C::kSub>(sKV + (uint32_t)((ldv % NS) * C::kStageBytes), lane, tail);
+          }
+          // one arrival per tile and block, then wait for the phase to complete before the next arrival on the same
+          // barrier: two arrivals of this warp must never fall into one phase
+#pragma unroll
+          for (int t = 0; t < NT; t++) {
+            if (j < w.nblk[t] && lane == 0) ptx::mbar_arrive(bar(kBarP0Ready + 2 * t + (C::kTwoPos ? (cnt[t] & 1) : 0)));
+          }
+#pragma unroll
+          for (int t = 0; t < NT; t++) {
+            if (j < w.nblk[t]) {
+              wait_bar(bar(kBarP0Ready + 2 * t + (C::kTwoPos ? (cnt[t] & 1) : 0)), (C::kTwoPos ? (cnt[t] >> 1) : cnt[t]) & 1, wc, 31);
+              cnt[t]++;
+            }
+          }
+        }
       }
     }
   }

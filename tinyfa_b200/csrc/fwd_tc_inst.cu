@@ -99,13 +99,14 @@ int TFA_NAME2(TFA_HDP, TFA_BF16)(const FwdProblem& pr, int packShift) {
 
   bool pair = false;  // clusters of two CTAs, one Q tile each, K/V shared (head dims 192 / 256, fixed length)
 #if TFA_HDP >= 192
-  // Measured (fp16, B8 H16, 800-launch loops, one-tile form -> pair form): head dim 256 non-causal S2048 872 -> 1168,
-  // S8192 957 -> 1244, causal S2048 760 -> 859 TFLOP/s; head dim 192 non-causal 1023 -> 1013, causal 826 -> 764 (three
-  // ring stages already keep its one-tile form fed).  Causal pairs pay for the fully masked last block of their first
-  // tile and, with short sequences, for item boundaries that are twice as heavy; "auto" is head dim 256 only, and its
-  // causal problems from 2048 query rows.
+  // Measured (fp16, H16, batch x length = 16 K tokens, 600-800-launch loops, one-tile form -> pair form): head dim 256
+  // non-causal S256 500 -> 497, S512 672 -> 789, S1024 791 -> 1010, S2048 872 -> 1168, S8192 957 -> 1244 TFLOP/s; causal
+  // S512 444 -> 432, S1024 611 -> 673, S1536 702 -> 813, S2048 760 -> 896; head dim 192 non-causal S2048 1023 -> 1013,
+  // S8192 1098 -> 1119, causal S2048 826 -> 764, S8192 1009 -> 1007 (three ring stages already keep its one-tile form
+  // fed).  Causal pairs pay for the fully masked last block of their first tile and, with short sequences, for item
+  // boundaries that are twice as heavy; "auto" is head dim 256 only, and its causal problems from 1024 query rows.
   const int pairOpt = option_pair_cta();
-  const bool pairAuto = (TFA_HDP == 256) && (!pr.causal || pr.seqLenQ >= 2048);
+  const bool pairAuto = (TFA_HDP == 256) && (!pr.causal || pr.seqLenQ >= 1024);
   pair = !varlen && pr.seqLenQ > (tc::kBlockM >> packShift) && (pairOpt > 0 || (pairOpt < 0 && pairAuto));
   if (pair) {
     kernel = tc::fwd_tc_kernel<TFA_HDP, kBf, tc::kModeFixed, false, TFA_HDP, true>;
