@@ -510,7 +510,8 @@ def test_rows_past_a_batch_entry_never_leak(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "fp16", "fp32"])
-@pytest.mark.parametrize("hd,causal", [(64, False), (128, False), (128, True), (256, False)])
+@pytest.mark.parametrize("hd,causal", [(32, True), (64, False), (96, False), (128, False), (128, True), (192, True), (256, False),
+                                       (256, True)])
 def test_packed_sequences_do_not_leak_into_each_other(hd, causal, dtype):
     """Packed variable-length input: a key block that reaches past the end of a sequence holds the NEXT sequence's
     rows.  NaN and Inf stored in that neighbour's K and V must not reach this sequence's output (the reference
@@ -537,6 +538,37 @@ def test_packed_sequences_do_not_leak_into_each_other(hd, causal, dtype):
         rows = slice(int(cu_q[b]), int(cu_q[b + 1]))
         assert np.isfinite(out[rows]).all()
         assert np.abs(out[rows] - ref[rows]).max() <= cases.MAXABS_TOL[dtype]
+
+
+@pytest.mark.parametrize("hd", [32, 64, 128, 192, 256])
+def test_many_short_packed_sequences_with_poisoned_neighbours(hd):
+    """Forty sequences of 1 to 200 tokens: almost every work item is a single, ragged key block, so the warp that
+    zeroes the V rows past a sequence's end meets ring stages that are still one or two uses behind.  Every second
+    sequence is NaN / Inf; the others must come out as if it held zeros."""
+    rng = np.random.default_rng(23 + hd)
+    lens = [int(x) for x in rng.integers(1, 201, 40)]
+    Hq, Hkv = 2, 1
+    Q, K, V, cu_q, cu_kv = _varlen_inputs(lens, lens, Hq, Hkv, hd, seed=5)
+    Qd, Kd, Vd = (torch.from_numpy(x).to(torch.bfloat16).cuda() for x in (Q, K, V))
+    for b in range(1, 40, 2):
+        Kd[cu_kv[b]:cu_kv[b + 1]] = float("nan")
+        Vd[cu_kv[b]:cu_kv[b + 1]] = float("inf")
+    cq, ck = torch.from_numpy(cu_q).cuda(), torch.from_numpy(cu_kv).cuda()
+    for causal in (False, True):
+        for _ in range(3):  # the ring position at a sequence's end differs from launch to launch
+            O = tf.flash_attn_varlen_forward(Qd, Kd, Vd, cq, ck, max(lens), max(lens), is_causal=causal)
+        Kc, Vc = Kd.clone(), Vd.clone()
+        for b in range(1, 40, 2):
+            Kc[cu_kv[b]:cu_kv[b + 1]] = 0
+            Vc[cu_kv[b]:cu_kv[b + 1]] = 0
+        ref = ao.varlen(Qd.float().cpu().numpy(), Kc.float().cpu().numpy(), Vc.float().cpu().numpy(), cu_q, cu_kv,
+                        causal, "f64")
+        out = O.float().cpu().numpy()
+        for b in range(0, 40, 2):
+            rows = slice(int(cu_q[b]), int(cu_q[b + 1]))
+            assert np.isfinite(out[rows]).all(), (hd, causal, b)
+            assert np.abs(out[rows] - ref[rows]).max() <= cases.MAXABS_TOL["bf16"], (hd, causal, b)
+    tf.device_status()
 
 
 @pytest.mark.parametrize("causal", [False, True])

@@ -16,7 +16,7 @@
 //   warps 8-11  epilogue: final 1/rowsum, conversion to the 16-bit type, stores O
 //   warp  12    issues the tcgen05.mma of Q tile 0 (one thread)
 //   warp  13    issues every TMA load (one thread)
-//   warp  14    idle
+//   warp  14    packed input: zeroes the V rows past a sequence's end; idle otherwise
 //   warp  15    issues the tcgen05.mma of Q tile 1 (one thread)
 //
 // Tensor memory columns (fp32 words per lane; lane = query row of the tile):
@@ -158,7 +158,7 @@ struct CfgSolo64 {
 // stages of 32 KB instead of 64 / 48 KB, i.e. room for four or five of them.  Tensor memory as in the one-tile form:
 // two S buffers and O.  At head dim 192 each CTA's half of V is 96 columns, one and a half 64-element slabs: CTA r
 // loads the slabs at head-dim offsets {0, 128} (r = 0) or {64, 160} (r = 1) and the MMA uses the first 96 columns, so
-// that the O columns come out permuted in chunks of 32 (kColMap); the output pass undoes it.
+// that the O columns come out permuted in chunks of 32 (o_chunk_offset); the output pass undoes it.
 template <int HDP>
 struct CfgPair {
   static_assert(HDP == 192 || HDP == 256, "pair form: head dims 192 and 256");
