@@ -82,7 +82,7 @@ STRONG_WORKLOADS = ("bf16_causal_gqa_b4_s8192_h32_8_d128", "bf16_causal_varlen_g
 NCU_TRAFFIC_BYTES = {
     "bf16_noncausal_b2_s4096_h32_d128": 247334144,
     "bf16_causal_b2_s4096_h32_d128": 266387456,
-    "bf16_causal_varlen_gqa_16seq_h32_8_d128": 1343037184,
+    "bf16_causal_varlen_gqa_16seq_h32_8_d128": 1342815744,
     "bf16_causal_gqa_b4_s8192_h32_8_d128": 644488192,
     "fp16_causal_b8_s2048_h16_d64": 114779392,
     "fp16_causal_b8_s2048_h16_d32": 52913664,
