@@ -89,7 +89,7 @@ NCU_TRAFFIC_BYTES = {
     "fp16_causal_b8_s2048_h16_d96": 184531200,
     "fp16_causal_b8_s2048_h16_d192": 386672128,
     "fp16_causal_b8_s2048_h16_d256": 524141824,
-    "fp32_noncausal_b2_s4096_h32_d128": 518427392,
+    "fp32_noncausal_b2_s4096_h32_d128": 519461120,
     "bf16_decode_b8_skv32768_h32_8_d128": 1078060032,
     "bf16_decode_b64_skv32768_h32_8_d128": 8624480256,
 }

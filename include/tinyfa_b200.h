@@ -90,6 +90,8 @@ int tfa_b200_device_status(int* site);
  *   "split_kv" -1/0/n  split-KV path for short query blocks (seqQ * group <= 16): auto / never / exactly n splits
  *   "narrow_mma" 0/1   head dims 32 / 96: MMAs of the padded width (64 / 128) / MMAs shaped for the head dim (the default)
  *   "solo64" 0/1       head dims 32 / 64: two-tile CTAs, one per SM / one-tile CTAs, two per SM (the default)
+ *   "fp32_t8" 0/1/2    fp32, head dim 128: 4 x 8 thread tiles always / 8 x 8 thread tiles for problems of at least three
+ *                      CTAs per SM (the default) / 8 x 8 always
  *   "pair_cta" -1/0/1  head dims 192 / 256, fixed-length input: clusters of two CTAs that work on two neighbouring query
  *                      tiles and share every K/V block through one MMA over both SMs (tcgen05 cta_group::2):
  *                      auto (head dim 256: non-causal, and causal from 1024 query rows; head dim 192: never, its

@@ -58,7 +58,7 @@ def test_status_codes_for_bad_arguments():
     assert lib.tfa_b200_set_option(b"no_such_option", 1) == 3
     assert lib.tfa_b200_set_option(b"pack_gqa", -1) == 0
     # every option the header documents is known to the library; -1 / 1 are their documented defaults
-    for name, default in ((b"split_kv", -1), (b"narrow_mma", 1), (b"solo64", 1), (b"pair_cta", -1), (b"work_order", -1)):
+    for name, default in ((b"split_kv", -1), (b"narrow_mma", 1), (b"solo64", 1), (b"pair_cta", -1), (b"fp32_t8", 1), (b"work_order", -1)):
         assert lib.tfa_b200_set_option(name, default) == 0, name
 
 

@@ -78,6 +78,8 @@ static std::atomic<int> g_optSolo64{1};  // head dims 32 / 64: one-tile CTAs, tw
 int option_solo64() { return g_optSolo64.load(); }
 static std::atomic<int> g_optPairCta{-1};  // head dims 192 / 256, fixed length: clusters of two CTAs sharing every K/V block (-1 auto)
 int option_pair_cta() { return g_optPairCta.load(); }
+static std::atomic<int> g_optFp32T8{1};  // fp32, head dim 128, large problems: the 8 x 8 thread-tile form
+int option_fp32_t8() { return g_optFp32T8.load(); }
 
 int next_epoch() { return (g_epoch.fetch_add(1) & 0x7FFFFF) + 1; }
 
@@ -564,6 +566,10 @@ extern "C" int tfa_b200_set_option(const char* name, int value) {
   }
   if (strcmp(name, "solo64") == 0) {
     g_optSolo64.store(value ? 1 : 0);
+    return kOk;
+  }
+  if (strcmp(name, "fp32_t8") == 0) {
+    g_optFp32T8.store(value < 0 ? 1 : (value > 2 ? 2 : value));
     return kOk;
   }
   if (strcmp(name, "pair_cta") == 0) {

@@ -22,6 +22,7 @@
 namespace tfa_b200 {
 
 int device_num_sms(int device);  // c_abi.cu
+int option_fp32_t8();             // c_abi.cu: 8 x 8 thread-tile form of the fp32 kernel at head dim 128
 
 struct Fp32Params {
   const float* Q;
@@ -581,6 +582,284 @@ int launch_lane(const FwdProblem& pr) {
   return kOk;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// 8 x 8 thread-tile form (D = 128): 128 query rows x 128 keys per block, 256 threads.  Thread (ty, tx) = (tid / 16,
+// tid % 16) owns rows 8 ty .. 8 ty + 7; in S the 8 columns tx + 16 i, in O the float4 chunks tx and tx + 16 of the head
+// dim.  Both products then fetch 16 values per 64 FMAs (the 4 x 8 form: 12 per 32 and 20 per 64), which is what takes
+// the kernel off the shared-memory roofline: a 16-byte shared-memory load is served a quarter warp at a time whatever
+// addresses coincide, so the only way to fewer shared-memory cycles per FMA is more FMAs per loaded value.
+//   * Q is transposed once per CTA (sQT[d][row]) and P is written transposed (sPT[key][row]), so that two neighbouring
+//     rows form a register pair: one fma.rn.f32x2 covers rows r, r + 1 against a duplicated K (V) value - no second
+//     set of partial sums, 64 + 64 accumulators per thread.
+//   * P is written over the K block it came from (a barrier between the two products), so three 66 KB buffers do:
+//     Q^T, K / P^T, V.  V(j) streams in under Q.K^T(j); K(j + 1) can only be requested after P.V(j) and is waited for at
+//     the top of the next block (about 1 of 20 us per block exposed; a 96-key variant with a P^T buffer of its own, which
+//     hides that load, measured 1 % slower).
+// Measured at B2 S4096 H32: 46.4 -> 49.4 TFLOP/s non-causal, 41.8 -> 44.4 causal; shared-memory data pipe 77 % -> 52 %
+// busy, FMA pipe 65 % -> 70 %; 255 registers, so the SM runs these 8 warps and no more, and what is left is latency that
+// two warps per scheduler do not cover.
+template <int D>
+__global__ void __launch_bounds__(256, 1) fwd_fp32_t8_kernel(const Fp32Params p) {
+  static_assert(D == 128, "8 x 8 form: head dim 128");
+  constexpr int BR = 128, BC = 128, kThreads = 256;
+  constexpr int NC = BC / 16;  // score columns per thread
+  constexpr int LDQ = BR + 4;  // sQT row pitch (a row of sQT holds one head-dim element of all 128 query rows)
+  constexpr int LD = D + 4;    // K / V row pitch
+  constexpr int LDP = BR + 4;  // sPT row pitch (a row holds one key's weights for all 128 query rows)
+  extern __shared__ float4 smemF4[];
+  float* sQT = reinterpret_cast<float*>(smemF4);
+  float* sK = sQT + D * LDQ;
+  float* sV = sK + BC * LD;
+  float* sPT = sK;  // aliased: P^T of block j overwrites K(j) once every warp is done with Q.K^T
+  static_assert(BC * LDP <= BC * LD, "P^T fits the K buffer");
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int hkv = h / p.group;
+  long long qRow0, kvRow0;
+  int sq, skv;
+  if (p.cuQ != nullptr) {
+    qRow0 = p.cuQ[b];
+    sq = p.cuQ[b + 1] - p.cuQ[b];
+    kvRow0 = p.cuKV[b];
+    skv = p.cuKV[b + 1] - p.cuKV[b];
+  } else {
+    sq = p.seqLenQ;
+    skv = p.seqLenKV;
+    qRow0 = (long long)b * sq;
+    kvRow0 = (long long)b * skv;
+  }
+  const int numTilesQ = gridDim.x;
+  const int tileIdx = p.causal ? (numTilesQ - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const int q0 = tileIdx * BR;
+  if (q0 >= sq || skv <= 0) return;
+  const int qEnd = min(q0 + BR, sq);
+  int nblk = (skv + BC - 1) / BC;
+  if (p.causal) nblk = min(nblk, (qEnd + BC - 1) / BC);
+
+  const long long qStride = (long long)p.headsQ * D;
+  const long long kvStride = (long long)p.headsKV * D;
+  const float* gQ = p.Q + (long long)h * D;
+  const float* gK = p.K + (long long)hkv * D;
+  const float* gV = p.V + (long long)hkv * D;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const int r0 = ty * 8;
+
+  // K(0) on its way, then Q transposed into shared memory (lanes walk rows: the transposed stores hit 32 banks)
+  load_tile<D, BC, LD, kThreads>(sK, gK, kvRow0, kvRow0 + skv, kvStride);
+  cp_async_commit();
+  for (int i = threadIdx.x; i < BR * (D / 4); i += kThreads) {
+    const int row = i % BR, d4 = i / BR;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (q0 + row < sq) v = *reinterpret_cast<const float4*>(gQ + (qRow0 + q0 + row) * qStride + d4 * 4);
+    sQT[(d4 * 4 + 0) * LDQ + row] = v.x;
+    sQT[(d4 * 4 + 1) * LDQ + row] = v.y;
+    sQT[(d4 * 4 + 2) * LDQ + row] = v.z;
+    sQT[(d4 * 4 + 3) * LDQ + row] = v.w;
+  }
+
+  float2 o[4][8];  // [row pair][head-dim column]: .x = row r0 + 2 rp, .y = the next row
+  float m[8], l[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+  }
+#pragma unroll
+  for (int rp = 0; rp < 4; rp++) {
+#pragma unroll
+    for (int cidx = 0; cidx < 8; cidx++) o[rp][cidx] = make_float2(0.f, 0.f);
+  }
+  const float c = p.scaleLog2;
+
+  for (int j = 0; j < nblk; j++) {
+    const int kbase = j * BC;
+    cp_async_wait<0>();  // K(j) has landed (and, for j = 0, nothing else is outstanding)
+    __syncthreads();     // ... for every thread; Q^T is visible; nobody still reads V(j - 1) or P^T(j - 1)
+    load_tile<D, BC, LD, kThreads>(sV, gV, kvRow0 + kbase, kvRow0 + skv, kvStride);
+    cp_async_commit();
+
+    // ---- S = Q K^T: rows r0 .. r0 + 7 as four register pairs, columns tx + 16 i
+    float2 acc[4][NC];
+#pragma unroll
+    for (int rp = 0; rp < 4; rp++) {
+#pragma unroll
+      for (int i = 0; i < NC; i++) acc[rp][i] = make_float2(0.f, 0.f);
+    }
+#pragma unroll 1
+    for (int d4 = 0; d4 < D / 4; d4++) {
+      float4 qa[4], qb[4];
+#pragma unroll
+      for (int dd = 0; dd < 4; dd++) {
+        qa[dd] = *reinterpret_cast<const float4*>(sQT + (d4 * 4 + dd) * LDQ + r0);
+        qb[dd] = *reinterpret_cast<const float4*>(sQT + (d4 * 4 + dd) * LDQ + r0 + 4);
+      }
+#pragma unroll
+      for (int i = 0; i < NC; i++) {
+        const float4 k = *reinterpret_cast<const float4*>(sK + (tx + 16 * i) * LD + d4 * 4);
+        const float kv[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+        for (int dd = 0; dd < 4; dd++) {
+          const float2 kd = make_float2(kv[dd], kv[dd]);
+          acc[0][i] = ffma2(make_float2(qa[dd].x, qa[dd].y), kd, acc[0][i]);
+          acc[1][i] = ffma2(make_float2(qa[dd].z, qa[dd].w), kd, acc[1][i]);
+          acc[2][i] = ffma2(make_float2(qb[dd].x, qb[dd].y), kd, acc[2][i]);
+          acc[3][i] = ffma2(make_float2(qb[dd].z, qb[dd].w), kd, acc[3][i]);
+        }
+      }
+    }
+    __syncthreads();  // every warp is done with K(j): its buffer becomes P^T(j)
+
+    // ---- mask + online softmax; P^T written as two float4 per column (8 consecutive rows)
+    const bool needMask = (kbase + BC > skv) || (p.causal && (kbase + BC - 1 > q0));
+    float scale[8], negMc[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      const int qpos = q0 + r0 + r;
+      int lim = BC;
+      if (needMask) {
+        lim = skv - kbase;
+        if (p.causal) lim = min(lim, qpos - kbase + 1);
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < NC; i++) {
+        float sv = (r & 1) ? acc[r >> 1][i].y : acc[r >> 1][i].x;
+        if (needMask && tx + 16 * i >= lim) sv = -INFINITY;
+        if (r & 1) {
+          acc[r >> 1][i].y = sv;
+        } else {
+          acc[r >> 1][i].x = sv;
+        }
+        mx = fmaxf(mx, sv);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      const float mNew = fmaxf(m[r], mx);
+      const float mUse = (mNew == -INFINITY) ? 0.f : mNew;
+      scale[r] = (m[r] == -INFINITY) ? 0.f : ex2((m[r] - mUse) * c);
+      m[r] = mNew;
+      negMc[r] = -mUse * c;
+    }
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+      float pv[8];
+#pragma unroll
+      for (int r = 0; r < 8; r++) {
+        const float sv = (r & 1) ? acc[r >> 1][i].y : acc[r >> 1][i].x;
+        pv[r] = ex2(fmaf(sv, c, negMc[r]));
+        sum[r] += pv[r];
+      }
+      float* dst = sPT + (tx + 16 * i) * LDP + r0;
+      *reinterpret_cast<float4*>(dst) = make_float4(pv[0], pv[1], pv[2], pv[3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; r++) l[r] = l[r] * scale[r] + sum[r];  // per-thread partial row sums, reduced over tx at the end
+#pragma unroll
+    for (int rp = 0; rp < 4; rp++) {
+      const float2 sc = make_float2(scale[2 * rp], scale[2 * rp + 1]);
+#pragma unroll
+      for (int cidx = 0; cidx < 8; cidx++) {
+        o[rp][cidx].x *= sc.x;
+        o[rp][cidx].y *= sc.y;
+      }
+    }
+
+    cp_async_wait<0>();  // V(j) has landed
+    __syncthreads();     // ... and P^T(j) is visible
+
+    // ---- O += P V: per key two float4 of P^T (8 rows) and two float4 of V (8 head-dim columns)
+#pragma unroll 2
+    for (int key = 0; key < BC; key++) {
+      const float4 pa = *reinterpret_cast<const float4*>(sPT + key * LDP + r0);
+      const float4 pb = *reinterpret_cast<const float4*>(sPT + key * LDP + r0 + 4);
+      const float4 va = *reinterpret_cast<const float4*>(sV + key * LD + tx * 4);
+      const float4 vb = *reinterpret_cast<const float4*>(sV + key * LD + 64 + tx * 4);
+      const float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+      for (int cidx = 0; cidx < 8; cidx++) {
+        const float2 vd = make_float2(vv[cidx], vv[cidx]);
+        o[0][cidx] = ffma2(make_float2(pa.x, pa.y), vd, o[0][cidx]);
+        o[1][cidx] = ffma2(make_float2(pa.z, pa.w), vd, o[1][cidx]);
+        o[2][cidx] = ffma2(make_float2(pb.x, pb.y), vd, o[2][cidx]);
+        o[3][cidx] = ffma2(make_float2(pb.z, pb.w), vd, o[3][cidx]);
+      }
+    }
+    __syncthreads();  // P^T(j) and V(j) are free again
+    if (j + 1 < nblk) load_tile<D, BC, LD, kThreads>(sK, gK, kvRow0 + kbase + BC, kvRow0 + skv, kvStride);
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+
+  // ---- normalise and store
+#pragma unroll
+  for (int r = 0; r < 8; r++) {
+    float sum = l[r];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+    const float inv = (sum > 0.f) ? (1.f / sum) : 0.f;
+    const int qpos = q0 + r0 + r;
+    if (qpos < sq) {
+      float* dst = p.O + (qRow0 + qpos) * qStride + (long long)h * D;
+      const int rp = r >> 1;
+      float4 a, bq;
+      if (r & 1) {
+        a = make_float4(o[rp][0].y * inv, o[rp][1].y * inv, o[rp][2].y * inv, o[rp][3].y * inv);
+        bq = make_float4(o[rp][4].y * inv, o[rp][5].y * inv, o[rp][6].y * inv, o[rp][7].y * inv);
+      } else {
+        a = make_float4(o[rp][0].x * inv, o[rp][1].x * inv, o[rp][2].x * inv, o[rp][3].x * inv);
+        bq = make_float4(o[rp][4].x * inv, o[rp][5].x * inv, o[rp][6].x * inv, o[rp][7].x * inv);
+      }
+      *reinterpret_cast<float4*>(dst + tx * 4) = a;
+      *reinterpret_cast<float4*>(dst + 64 + tx * 4) = bq;
+    }
+  }
+}
+
+template <int D>
+int launch_t8(const FwdProblem& pr) {
+  constexpr int kSmem = (D * (128 + 4) + 2 * 128 * (D + 4)) * (int)sizeof(float);
+  auto kernel = fwd_fp32_t8_kernel<D>;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return kCudaError;
+  static std::once_flag once[64];
+  static cudaError_t attrErr[64];
+  std::call_once(once[device], [&] {
+    attrErr[device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  });
+  if (attrErr[device] != cudaSuccess) {
+    set_error_string("cudaFuncSetAttribute(%d bytes): %s", kSmem, cudaGetErrorString(attrErr[device]));
+    return kCudaError;
+  }
+  Fp32Params p;
+  p.Q = static_cast<const float*>(pr.Q);
+  p.K = static_cast<const float*>(pr.K);
+  p.V = static_cast<const float*>(pr.V);
+  p.O = static_cast<float*>(pr.O);
+  p.cuQ = pr.cuQ;
+  p.cuKV = pr.cuKV;
+  p.seqLenQ = pr.seqLenQ;
+  p.seqLenKV = pr.seqLenKV;
+  p.headsQ = pr.headsQ;
+  p.headsKV = pr.headsKV;
+  p.group = pr.headsQ / pr.headsKV;
+  p.causal = pr.causal;
+  p.scaleLog2 = (float)(1.4426950408889634 / sqrt((double)D));
+  dim3 grid((unsigned)((pr.seqLenQ + 127) / 128), (unsigned)pr.headsQ, (unsigned)pr.batch);
+  kernel<<<grid, 256, kSmem, pr.stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error_string("fp32 kernel launch failed: %s", cudaGetErrorString(e));
+    return kCudaError;
+  }
+  return kOk;
+}
+
 template <int D, int BR>
 int launch(const FwdProblem& pr) {
   constexpr int LD = D + 4;
@@ -647,7 +926,11 @@ int launch_fwd_fp32(const FwdProblem& pr) {
         int device = 0;
         cudaGetDevice(&device);
         const long long ctas128 = (long long)((pr.seqLenQ + 127) / 128) * pr.headsQ * pr.batch;
-        if (ctas128 >= 3LL * device_num_sms(device)) return fp32::launch<128, 128>(pr);
+        const int t8 = option_fp32_t8();  // 0 never, 1 for large problems (the default), 2 always (tests)
+        if (t8 == 2) return fp32::launch_t8<128>(pr);
+        if (ctas128 >= 3LL * device_num_sms(device)) {
+          return t8 != 0 ? fp32::launch_t8<128>(pr) : fp32::launch<128, 128>(pr);
+        }
       }
       return fp32::launch<128, 64>(pr);
 #endif
