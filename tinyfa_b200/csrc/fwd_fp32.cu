@@ -772,7 +772,7 @@ __global__ void __launch_bounds__(256, 1) fwd_fp32_t8_kernel(const Fp32Params p)
     __syncthreads();     // ... and P^T(j) is visible
 
     // ---- O += P V: per key two float4 of P^T (8 rows) and two float4 of V (8 head-dim columns)
-#pragma unroll 2
+#pragma unroll 4
     for (int key = 0; key < BC; key++) {
       const float4 pa = *reinterpret_cast<const float4*>(sPT + key * LDP + r0);
       const float4 pb = *reinterpret_cast<const float4*>(sPT + key * LDP + r0 + 4);
